@@ -51,6 +51,7 @@ def host_library():
             getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p]
         for name in ("release", "unreserve", "n_free_pages"):
             getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p, c_int]
+        lib.llmx_alloc_set_keep_first.argtypes = [c_void_p, c_int, c_int]
         for name in ("reserve", "commit"):
             getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p, c_int, c_longlong]
         lib.llmx_alloc_commit_many.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
@@ -86,9 +87,11 @@ def raise_host_error(code: int) -> None:
 
 
 class CacheAllocator:
-    """Slots, pages and lengths.  ``windows[g]`` is group g's window or None."""
+    """Slots, pages and lengths.  ``windows[g]`` is group g's window or None; ``keep_first[g]`` how many of a
+    sequence's first positions stay visible under the window (their pages are never given back)."""
 
-    def __init__(self, n_slots: int, n_pages: int, windows: list, max_seq_len: Optional[int] = None):
+    def __init__(self, n_slots: int, n_pages: int, windows: list, max_seq_len: Optional[int] = None,
+                 keep_first: Optional[list] = None):
         if n_slots <= 0 or n_pages <= 0:
             raise ValueError("the cache needs at least one slot and one page")
         self.n_slots, self.n_pages = n_slots, n_pages
@@ -99,6 +102,10 @@ class CacheAllocator:
         self._h = self._lib.llmx_alloc_new(n_slots, n_pages, w, len(self.windows), self.max_seq_len)
         if not self._h:
             raise ValueError("the cache needs at least one slot, one page and one group")
+        self.keep_first = [int(x or 0) for x in (keep_first or [0] * len(self.windows))]
+        for g, n in enumerate(self.keep_first):
+            if n:
+                self._ok(self._lib.llmx_alloc_set_keep_first(self._h, g, n))
         self._row = (c_int * max(1, n_pages))()
 
     def __del__(self):

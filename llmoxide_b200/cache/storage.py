@@ -25,7 +25,8 @@ from .allocator import PAGE, CacheAllocator
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values for every position (window None) or for the last
-    ``window`` positions.  Values may be narrower or wider than keys
+    ``window`` positions, beside which the first ``keep_first`` positions of a
+    sequence stay visible for good.  Values may be narrower or wider than keys
     (``v_head_dim``, default ``head_dim``), and an entry may keep its keys and
     values in a dtype of its own (default: the runtime's cache dtype)."""
 
@@ -34,6 +35,7 @@ class KVNeed:
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -90,7 +92,8 @@ class Cache:
             for e, (_, st) in enumerate(needs)
         ]
         self.alloc = CacheAllocator(n_slots, n_pages, [kv.window for kv in self.groups] or [None],
-                                    max_seq_len=max_seq_len)
+                                    max_seq_len=max_seq_len,
+                                    keep_first=[kv.keep_first for kv in self.groups] or [0])
         self._has_groups = bool(self.groups)
 
     # ---- slots -------------------------------------------------------------

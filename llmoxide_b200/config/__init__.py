@@ -3,11 +3,13 @@ description that the rest of the package reads."""
 
 from .qwen3 import Qwen3Config
 from .registry import architectures, config_class, read_config, register_architecture
+from .tifapel import TifapelConfig
 from .spec import BlockSpec, LayerCall, ModelSpec, PartSpec, TensorSpec, default_schedule
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
+register_architecture("Tifapel", TifapelConfig)
 
 __all__ = [
-    "Qwen3Config", "architectures", "config_class", "read_config", "register_architecture",
+    "Qwen3Config", "TifapelConfig", "architectures", "config_class", "read_config", "register_architecture",
     "BlockSpec", "LayerCall", "ModelSpec", "PartSpec", "TensorSpec", "default_schedule",
 ]

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json ``architectures[0]``)
+"""One registry from an architecture's name (config.json ``architectures[0]``, or the string ``architecture``)
 to its typed configuration.  The reference maps ``general.architecture`` to an
 enum the same way and refuses unknown names (crates/model/src/lib.rs:37-54).
 """
@@ -31,9 +31,11 @@ def config_class(name: str):
 
 def architecture_name(raw: dict) -> str:
     names = raw.get("architectures")
-    if not names or not isinstance(names, (list, tuple)) or not isinstance(names[0], str):
-        raise ConfigError("config.json has no 'architectures' entry naming the model")
-    return names[0]
+    if names and isinstance(names, (list, tuple)) and isinstance(names[0], str):
+        return names[0]
+    if isinstance(raw.get("architecture"), str):      # some designs name themselves with one string
+        return raw["architecture"]
+    raise ConfigError("config.json has no 'architectures' (or 'architecture') entry naming the model")
 
 
 def read_config(source):

@@ -7,13 +7,17 @@
 // kv head g = hq / (H/G); keys first..p are visible, first = 0 or p-(w-1) under
 // a window (crates/model/src/cache.rs:31-37); s_j = (q . k_j) * scale; softmax
 // with the maximum subtracted; out = sum_j w_j v_j.  All of it in float32.
+// With `keep_first` > 0 the keys 0..keep_first-1 stay visible under the window
+// as well (they are taken first, then the window's keys).  Values may have a
+// size Dv of their own; a query row may sit in a wider row (q_stride elements
+// from token to token), e.g. the q|k|v row of a fused product.
 //
-// One warp per (token, head).  Keys are taken 32 at a time starting at
-// `first`: lane j scores key first + c*32 + j with a sequential dot over D,
-// the chunk's maximum and sum update a running softmax, and the lanes then
+// One warp per (token, head).  Keys are taken 32 at a time starting at the
+// range's first key: lane j scores key lo + c*32 + j with a sequential dot over
+// D, the chunk's maximum and sum update a running softmax, and the lanes then
 // own dims (lane, lane+32, ...) of the output and add the chunk's values key
-// by key.  Chunk boundaries depend on (first, p) only, so a position's result
-// does not depend on how tokens were cut into steps or batched.
+// by key.  Chunk boundaries depend on (keep_first, first, p) only, so a
+// position's result does not depend on how tokens were cut into steps or batched.
 #include "common.cuh"
 
 #define ATT_WARPS 4
@@ -24,7 +28,8 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
                                        const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                                        const int* __restrict__ block_table, int table_width,
                                        const int* __restrict__ token_seq, const int* __restrict__ token_pos,
-                                       int H, int G, int D, int window, float scale) {
+                                       int H, int G, int D, int Dv, size_t q_stride, int window, int keep_first,
+                                       float scale) {
   extern __shared__ float q_buf[];  // [ATT_WARPS][D]
   pdl_launch_dependents();
   pdl_wait();
@@ -38,7 +43,7 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   const int* pages = block_table + (size_t)token_seq[t] * table_width;
 
   float* qs = q_buf + warp * D;
-  const TA* qrow = q + ((size_t)t * H + hq) * D;
+  const TA* qrow = q + (size_t)t * q_stride + (size_t)hq * D;
   for (int i = lane; i < D; i += 32) qs[i] = to_f32(qrow[i]);
   __syncwarp();
 
@@ -48,9 +53,13 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   for (int i = 0; i < MAX_OWN; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
 
-  for (int base = first; base <= p; base += 32) {
+  // two ranges of keys: the kept first ones that lie before the window, then the window up to p
+  const int n_kept = keep_first < first ? keep_first : first;
+  for (int range = n_kept > 0 ? 0 : 1; range < 2; ++range) {
+  const int lo = range ? first : 0, last = range ? p : n_kept - 1;
+  for (int base = lo; base <= last; base += 32) {
     const int j = base + lane;
-    const bool live = j <= p;
+    const bool live = j <= last;
     float s = -INFINITY;
     if (live) {
       const TC* krow = k_cache + cache_row_offset(pages[j / LLMX_PAGE], g, j % LLMX_PAGE, G, D);
@@ -59,45 +68,48 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
       s = dot * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
-    const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first chunk; lane 0 is always live
+    const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first chunk; lane 0 of a chunk is always live
     const float e = live ? expf(s - m_new) : 0.f;
     l = l * corr + warp_sum(e);
 #pragma unroll
     for (int i = 0; i < MAX_OWN; ++i) acc[i] *= corr;
-    const int n_live = (p - base + 1) < 32 ? (p - base + 1) : 32;
+    const int n_live = (last - base + 1) < 32 ? (last - base + 1) : 32;
     for (int jj = 0; jj < n_live; ++jj) {
       const float w = __shfl_sync(0xffffffffu, e, jj);
       const int key = base + jj;
-      const TC* vrow = v_cache + cache_row_offset(pages[key / LLMX_PAGE], g, key % LLMX_PAGE, G, D);
+      const TC* vrow = v_cache + cache_row_offset(pages[key / LLMX_PAGE], g, key % LLMX_PAGE, G, Dv);
 #pragma unroll
       for (int i = 0; i < MAX_OWN; ++i) {
         const int dim = lane + 32 * i;
-        if (dim < D) acc[i] += w * to_f32(vrow[dim]);
+        if (dim < Dv) acc[i] += w * to_f32(vrow[dim]);
       }
     }
     m = m_new;
   }
+  }
   const float inv = 1.0f / l;
-  TA* orow = out + ((size_t)t * H + hq) * D;
+  TA* orow = out + ((size_t)t * H + hq) * Dv;
 #pragma unroll
   for (int i = 0; i < MAX_OWN; ++i) {
     const int dim = lane + 32 * i;
-    if (dim < D) orow[dim] = from_f32<TA>(acc[i] * inv);
+    if (dim < Dv) orow[dim] = from_f32<TA>(acc[i] * inv);
   }
 }
 
 LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const void* k_cache,
                                   const void* v_cache, int cache_dtype, const int* block_table, int table_width,
                                   const int* token_seq, const int* token_pos, int n_tokens, int H, int G, int D,
-                                  int window, float scale, cudaStream_t stream) {
+                                  int Dv, long long q_stride, int window, int keep_first, float scale,
+                                  cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || D > ATT_MAX_D || window < 0) return LLMX_REFUSED(1);
+  if (Dv <= 0 || Dv > ATT_MAX_D || keep_first < 0 || q_stride < (long long)H * D) return LLMX_REFUSED(1);
   dim3 grid(n_tokens, (H + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = (size_t)ATT_WARPS * D * sizeof(float);
 #define CASE(TA, TC)                                                                                      \
   launch_pdl(attention_paged_kernel<TA, TC>, grid, dim3(ATT_WARPS * 32), smem, stream,                    \
       (const TA*)q, (TA*)out, (const TC*)k_cache, (const TC*)v_cache, block_table, table_width, token_seq, \
-      token_pos, H, G, D, window, scale)
+      token_pos, H, G, D, Dv, (size_t)q_stride, window, keep_first, scale)
   if (act_dtype == LLMX_F32 && cache_dtype == LLMX_F32) CASE(float, float);
   else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) CASE(bf16, bf16);
   else if (act_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) CASE(float, bf16);

@@ -41,6 +41,8 @@ LIBRARIES = {
     "attention_prefill_tc": (["attention_prefill_tc.cu"], []),
     "gemm_fma": (["gemm_fma.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
+    "linear_attention": (["linear_attention.cu"], []),
+    "moe": (["moe.cu"], []),
     "sampling": (["sampling.cu"], []),
     "random_init": (["random_init.cu"], []),
     # host code only (no CUDA): the cache's bookkeeping and the step plan

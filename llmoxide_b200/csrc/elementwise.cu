@@ -337,7 +337,7 @@ LLMX_API int llmx_add_gain_sumsq(float* h, const void* delta, int delta_dtype, i
 
 // ---------------------------------------------------------------------------
 // Per-head RMSNorm of q and k, NeoX rotation of both, and the cache write of
-// k and v.  Input qkv [T, (H+2G)*D]: q heads, then k heads, then v heads.
+// k and v.  Input qkv [T, (H+G)*D + G*Dv]: q heads, then k heads (size D), then v heads (size Dv).
 // One warp per (token, head).  The normalised head is staged in shared memory
 // so that a dim can read its rotation partner (i, i + n_rot/2) at any D.
 // cos/sin tables are [max_pos, n_rot/2] float32, made on the host in float64.
@@ -358,7 +358,7 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
                                           const float* __restrict__ q_gain, const float* __restrict__ k_gain,
                                           float eps, const float* __restrict__ cos_t,
                                           const float* __restrict__ sin_t, int n_rot, int H, int G, int D,
-                                          int write_cache) {
+                                          int Dv, int write_cache) {
   constexpr int SPW = DEEP ? 1 : QKV_SPW;
   extern __shared__ float head_buf[];
   pdl_launch_dependents();
@@ -370,16 +370,17 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
   const int n_slots = write_cache ? H + 2 * G : H;
   if (slot0 >= n_slots) return;
   float* buf = head_buf + warp * D;
-  const TIN* tok = qkv + (size_t)t * (H + 2 * G) * D;
+  const TIN* tok = qkv + (size_t)t * ((size_t)(H + G) * D + (size_t)G * Dv);   // q heads, k heads (D each), v heads (Dv each)
   const int pos = token_pos[t];
   int page = 0;
   if (slot0 + SPW > H) page = block_table[(size_t)token_seq[t] * table_width + pos / LLMX_PAGE];
   auto cache_row_of = [&](int slot) -> TC* {        // slot >= H: a k head, then the v heads
     const bool is_k = slot < H + G;
-    return (is_k ? k_cache : v_cache) + cache_row_offset(page, is_k ? slot - H : slot - H - G, pos % LLMX_PAGE, G, D);
+    return is_k ? k_cache + cache_row_offset(page, slot - H, pos % LLMX_PAGE, G, D)
+                : v_cache + cache_row_offset(page, slot - H - G, pos % LLMX_PAGE, G, Dv);
   };
 
-  if (D == 128 && n_rot == 128) {
+  if (D == 128 && n_rot == 128 && Dv == 128) {
     // Head size 128 with full rotation: a lane owns dims 4*lane..4*lane+3, read and written as one
     // vector; the rotation partner (dim +-64) lives in lane +-16 and comes by shuffle.
     const int d0 = 4 * lane;
@@ -433,7 +434,7 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
   for (int j = 0; j < SPW; ++j) {
     const int slot = slot0 + j;
     if (slot >= n_slots) break;
-    const TIN* src = tok + (size_t)slot * D;
+    const TIN* src = slot < H + G ? tok + (size_t)slot * D : tok + (size_t)(H + G) * D + (size_t)(slot - H - G) * Dv;
     // the head's values: one tensor, or split partials added in order
     auto value = [&](int i) {
       float v = to_f32(src[i]);
@@ -443,7 +444,7 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
     const bool is_q = slot < H, is_k = !is_q && slot < H + G;
     TC* cache_row = is_q ? nullptr : cache_row_of(slot);
     if (!is_q && !is_k) {  // v: stored as it is
-      for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(value(i));
+      for (int i = lane; i < Dv; i += 32) cache_row[i] = from_f32<TC>(value(i));
       continue;
     }
     const float* gain = is_q ? q_gain : k_gain;
@@ -584,13 +585,13 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
                                      const int* block_table, int table_width, const int* token_seq,
                                      const int* token_pos, const float* q_gain, const float* k_gain, float eps,
                                      const float* cos_t, const float* sin_t, int n_rot, int n_tokens, int H, int G,
-                                     int D, int write_cache, cudaStream_t stream) {
+                                     int D, int Dv, int write_cache, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (H <= 0 || G <= 0 || D <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1) return LLMX_REFUSED(1);
+  if (H <= 0 || G <= 0 || D <= 0 || Dv <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1) return LLMX_REFUSED(1);
   if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
   const int n_slots = write_cache ? H + 2 * G : H;
   if (n_split == 1 && in_dtype == LLMX_BF16 && act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16 && D == 128 &&
-      n_rot == 128 && n_tokens > 64 && !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
+      Dv == 128 && n_rot == 128 && n_tokens > 64 && !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
     const int per_cta = QKV_WARPS * QKV8_PER_WARP;
     launch_pdl(qk_norm_rope_cache_bf16_d128_kernel, dim3(n_tokens, (n_slots + per_cta - 1) / per_cta),
                dim3(QKV_WARPS * 32), 0, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache,
@@ -608,11 +609,11 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
     if (deep)                                                                                                      \
       launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC, true>, grid, dim3(QKV_WARPS * 32), smem, stream,           \
         (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,        \
-        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache);         \
+        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, Dv, write_cache);     \
     else                                                                                                           \
       launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC, false>, grid, dim3(QKV_WARPS * 32), smem, stream,          \
         (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,        \
-        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache);         \
+        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, Dv, write_cache);     \
   } while (0)
   const int key = in_dtype * 4 + act_dtype * 2 + cache_dtype;
   switch (key) {

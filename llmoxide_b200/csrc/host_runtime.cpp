@@ -71,12 +71,13 @@ struct Allocator {
   int n_slots, n_pages;
   long long max_seq_len;
   std::vector<int> windows;                  // per group; <= 0: every earlier key
+  std::vector<int> keep_first;               // per group with a window: the first positions stay visible for good
   std::vector<Pool> pools;
   std::vector<Slot> slots;
   std::vector<int> free_slots;               // back() is handed out next
 
   Allocator(int ns, int np, const int* w, int ng, long long max_len)
-      : n_slots(ns), n_pages(np), max_seq_len(max_len), windows(w, w + ng), slots(ns) {
+      : n_slots(ns), n_pages(np), max_seq_len(max_len), windows(w, w + ng), keep_first(ng, 0), slots(ns) {
     for (int g = 0; g < ng; ++g) pools.emplace_back(np);
     for (int s = ns - 1; s >= 0; --s) free_slots.push_back(s);
   }
@@ -156,7 +157,8 @@ struct Allocator {
   }
 
   // The step wrote n_new positions: the length grows, and groups with a window give back the pages that no
-  // later query can see (the next query sits at `length` and sees keys from length - (window - 1) on).
+  // later query can see (the next query sits at `length` and sees keys from length - (window - 1) on, and the
+  // group's first `keep_first` positions whatever its own position: their pages are never given back).
   int commit(int slot, long long n_new) {
     Slot* st = live(slot);
     if (!st) return MISUSE;
@@ -168,7 +170,7 @@ struct Allocator {
       if (windows[g] <= 0) continue;
       const long long first_visible = std::max(0LL, st->length - (windows[g] - 1));
       const long long dead = std::min<long long>(first_visible / LLMX_PAGE, (long long)st->pages[g].size());
-      for (long long i = 0; i < dead; ++i)
+      for (long long i = pages_for(keep_first[g]); i < dead; ++i)
         if (st->pages[g][i] >= 0) {
           if (pools[g].give_back(st->pages[g][i])) return MISUSE;
           st->pages[g][i] = -1;
@@ -308,6 +310,13 @@ LLMX_API int llmx_host_error(char* out, int cap, long long* info) {
 LLMX_API void* llmx_alloc_new(int n_slots, int n_pages, const int* windows, int n_groups, long long max_seq_len) {
   if (n_slots <= 0 || n_pages <= 0 || n_groups <= 0) return nullptr;
   return new Allocator(n_slots, n_pages, windows, n_groups, max_seq_len);
+}
+// The first n positions of every sequence stay visible in a group with a window (set before any sequence is live).
+LLMX_API int llmx_alloc_set_keep_first(void* a, int group, int n) {
+  Allocator* al = static_cast<Allocator*>(a);
+  if (group < 0 || group >= (int)al->keep_first.size() || n < 0) return fail(BAD_VALUE, "no group %d, or a negative count", group);
+  al->keep_first[group] = n;
+  return OK;
 }
 LLMX_API void llmx_alloc_delete(void* a) { delete static_cast<Allocator*>(a); }
 LLMX_API int llmx_alloc_acquire(void* a) { return static_cast<Allocator*>(a)->acquire(); }      // slot, or -code

@@ -1,0 +1,303 @@
+// Routed experts (a mixture of small gated feed-forward layers of which each token uses a few).
+//
+//   route      per token: scores from the router's float32 logits, the groups of experts a token may choose
+//              from, its `top` experts and their weights
+//   sort       the step's (token, choice) pairs ordered by expert, and the list of row tiles per expert
+//   grouped products on the sorted rows: gate|up with the gated activation, then down times the pair's weight
+//
+// Everything a token gets depends on that token alone: routing is per token, and every output element of the
+// products is accumulated by one thread in the order k = 0..K-1 whatever tile the row falls into, so results
+// do not depend on what else is in the batch or on how a prompt was cut.  The order of rows inside an
+// expert's segment is whatever the sort's atomics gave; no value depends on it.
+#include "common.cuh"
+
+#define MOE_TILE 64          // rows (and columns) per tile of the grouped products
+#define MOE_BK 16
+#define MOE_MAX_TOP 16
+#define MOE_MAX_EXPERTS 1024
+
+enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1 };
+
+// ---------------------------------------------------------------------------
+// Routing.  One warp per token.  scores s = sigmoid(z) (or softmax(z)); experts form n_groups equal groups of
+// neighbours; a group's score is the sum of its `group_top` largest scores; only experts of the `keep_groups`
+// best groups can be chosen; the `top` largest scores among them are chosen (ties: the lower index); weights
+// are the chosen scores, divided by their sum + norm_eps when `normalize`, times `scale`.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+    if (v2 > v || (v2 == v && i2 < i)) v = v2, i = i2;
+  }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
+                                 int n_tokens, int E, int top, int n_groups, int keep_groups, int group_top,
+                                 int score_kind, int normalize, float norm_eps, float scale) {
+  extern __shared__ float route_smem[];            // per warp: E scores, then n_groups group scores
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  float* s = route_smem + warp * (E + n_groups);
+  float* gs = s + E;
+  const float* z = logits + (size_t)t * E;
+  if (score_kind == MOE_SCORE_SOFTMAX) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) s[e] = expf(z[e] - m) / sum;
+  } else {
+    for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-z[e]));
+  }
+  __syncwarp();
+  const int per = E / n_groups;
+  if (n_groups > 1 && keep_groups < n_groups) {
+    // a group's score: the sum of its group_top largest (picked one by one; an index picked is left out)
+    for (int g = lane; g < n_groups; g += 32) {
+      int picked[8];
+      float sum = 0.f;
+      const int n_pick = group_top < per ? group_top : per;
+      for (int k = 0; k < n_pick; ++k) {
+        float best = -INFINITY;
+        int bi = -1;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          bool used = false;
+          for (int j = 0; j < k; ++j) used = used || picked[j] == e;
+          if (!used && s[e] > best) best = s[e], bi = e;
+        }
+        picked[k] = bi;
+        sum += best;
+      }
+      gs[g] = sum;
+    }
+    __syncwarp();
+    // the keep_groups best groups stay; the others' experts get a score no expert can have
+    for (int k = 0; k < keep_groups; ++k) {
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32)
+        if (gs[g] > best) best = gs[g], bi = g;     // ascending g: the lower index wins a tie
+      warp_argmax(best, bi);
+      if (lane == 0) gs[bi] = -INFINITY;            // kept: marked
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / per] != -INFINITY) s[e] = -1.0f;   // not kept
+    __syncwarp();
+  }
+  float sum = 0.f, mine = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (s[e] > best) best = s[e], bi = e;
+    warp_argmax(best, bi);
+    if (lane == 0) s[bi] = -2.0f;                   // chosen: out of the running
+    __syncwarp();
+    if (lane == k) mine = best, my_id = bi;
+    sum += best;
+  }
+  if (lane < top) {
+    const float w = normalize ? mine / (sum + norm_eps) : mine;
+    ids[(size_t)t * top + lane] = my_id;
+    wts[(size_t)t * top + lane] = w * scale;
+  }
+}
+
+LLMX_API int llmx_moe_route(const float* logits, int* ids, float* wts, int n_tokens, int E, int top, int n_groups,
+                            int keep_groups, int group_top, int score_kind, int normalize, float norm_eps,
+                            float scale, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || top > 32 || n_groups <= 0 || E % n_groups ||
+      keep_groups <= 0 || keep_groups > n_groups || group_top <= 0 || group_top > 8 ||
+      top > E / n_groups * keep_groups)
+    return LLMX_REFUSED(1);
+  const size_t smem = 4 * (size_t)(E + n_groups) * sizeof(float);
+  launch_pdl(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), smem, stream, logits, ids, wts, n_tokens, E, top,
+             n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale);
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Sort.  One CTA.  P = n_tokens * top pairs, pair r = t * top + choice.  Out: perm[P] (sorted place -> pair),
+// tiles: for every row tile of MOE_TILE sorted rows that lie in one expert's segment, (expert, first row,
+// number of rows); unused tiles have expert -1.  max_tiles >= P / MOE_TILE + E.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ perm, int* __restrict__ tiles,
+                int max_tiles) {
+  __shared__ int count[MOE_MAX_EXPERTS];
+  __shared__ int start[MOE_MAX_EXPERTS + 1];
+  __shared__ int tile0[MOE_MAX_EXPERTS + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int r = tid; r < P; r += blockDim.x) atomicAdd(&count[ids[r]], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0, tl = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at;
+      tile0[e] = tl;
+      at += count[e];
+      tl += (count[e] + MOE_TILE - 1) / MOE_TILE;
+    }
+    start[E] = at;
+    tile0[E] = tl;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    const int n = count[e];
+    for (int k = 0, tl = tile0[e]; k < n; k += MOE_TILE, ++tl) {
+      tiles[3 * tl] = e;
+      tiles[3 * tl + 1] = start[e] + k;
+      tiles[3 * tl + 2] = (n - k) < MOE_TILE ? (n - k) : MOE_TILE;
+    }
+    count[e] = 0;          // reused as the segment's fill counter
+  }
+  for (int tl = tile0[E] + tid; tl < max_tiles; tl += blockDim.x) tiles[3 * tl] = -1;
+  __syncthreads();
+  for (int r = tid; r < P; r += blockDim.x) {
+    const int e = ids[r];
+    perm[start[e] + atomicAdd(&count[e], 1)] = r;
+  }
+}
+
+LLMX_API int llmx_moe_sort(const int* ids, int P, int E, int* perm, int* tiles, int max_tiles, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_EXPERTS || max_tiles < (P + MOE_TILE - 1) / MOE_TILE + E) return LLMX_REFUSED(1);
+  launch_pdl(moe_sort_kernel, dim3(1), dim3(P >= 4096 ? 1024 : 256), 0, stream, ids, P, E, perm, tiles, max_tiles);
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Grouped products on the FMA units (float32 accumulation, k = 0..K-1 per output element).
+//
+// GATED: rows are tokens' rows of x gathered through perm (token = pair / top); W = [E][2F][K], gate rows then
+//   up rows; out act[place][f] = silu(gate) * up, in sorted order.
+// else:  rows are act[place]; W = [E][N][K]; out y[choice][token][n] = weight[pair] * sum, float32: one partial
+//   per choice, which whoever adds them to the residual stream sums in the order of the choices.
+// ---------------------------------------------------------------------------
+template <typename TX, typename TW, typename TY, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_fma_kernel(const TX* __restrict__ X, long long ldx, const TW* __restrict__ W, TY* __restrict__ Y,
+                       const int* __restrict__ perm, const int* __restrict__ tiles,
+                       const float* __restrict__ pair_weight, int top, int n_tokens, int N, int K) {
+  __shared__ float Xs[MOE_BK][MOE_TILE + 4];
+  __shared__ float Ws[MOE_BK][MOE_TILE + 4];
+  __shared__ float Us[GATED ? MOE_BK : 1][MOE_TILE + 4];
+  __shared__ int row_src[MOE_TILE];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tl = blockIdx.y;
+  const int e = tiles[3 * tl];
+  if (e < 0) return;
+  const int row0 = tiles[3 * tl + 1], n_rows = tiles[3 * tl + 2];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int n0 = blockIdx.x * MOE_TILE;
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;
+  if (tid < MOE_TILE) row_src[tid] = tid < n_rows ? perm[row0 + tid] : -1;
+  __syncthreads();
+  const int pair = row_src[lrow];
+  const TX* xrow = nullptr;
+  if (pair >= 0) xrow = GATED ? X + (size_t)(pair / top) * ldx : X + (size_t)(row0 + lrow) * ldx;
+  const size_t w_rows = GATED ? 2 * (size_t)N : (size_t)N;
+  const TW* We = W + (size_t)e * w_rows * K;
+  const int n_load = n0 + lrow;
+  const TW* wrow = n_load < N ? We + (size_t)n_load * K : nullptr;
+  const TW* urow = (GATED && n_load < N) ? We + ((size_t)N + n_load) * K : nullptr;
+
+  float acc[4][4], acu[GATED ? 4 : 1][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[i][j] = 0.f;
+      if constexpr (GATED) acu[i][j] = 0.f;
+    }
+  for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int k = k0 + lk + c;
+      Xs[lk + c][lrow] = (xrow && k < K) ? to_f32(xrow[k]) : 0.f;
+      Ws[lk + c][lrow] = (wrow && k < K) ? to_f32(wrow[k]) : 0.f;
+      if constexpr (GATED) Us[lk + c][lrow] = (urow && k < K) ? to_f32(urow[k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MOE_BK; ++kk) {
+      float a[4], b[4], u[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = Xs[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        b[j] = Ws[kk][tx * 4 + j];
+        if constexpr (GATED) u[j] = Us[kk][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          if constexpr (GATED) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lr = ty * 4 + i;
+    const int pr = row_src[lr];
+    if (pr < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      if constexpr (GATED) {
+        const float g = acc[i][j];
+        Y[(size_t)(row0 + lr) * N + n] = from_f32<TY>(g / (1.0f + expf(-g)) * acu[i][j]);
+      } else {
+        const int t = pr / top, choice = pr - t * top;
+        Y[((size_t)choice * n_tokens + t) * N + n] = from_f32<TY>(pair_weight[pr] * acc[i][j]);
+      }
+    }
+  }
+}
+
+// gated != 0: X = x [n_tokens, K] (row stride ldx), W [E, 2N, K], Y = act [P, N].
+// else:       X = act [P, K], W [E, N, K], Y = float32 [top, n_tokens, N].
+LLMX_API int llmx_moe_grouped_fma(const void* X, int x_dtype, long long ldx, const void* W, int w_dtype, void* Y,
+                                  int y_dtype, const int* perm, const int* tiles, int max_tiles,
+                                  const float* pair_weight, int top, int n_tokens, int N, int K, int gated,
+                                  cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (N <= 0 || K <= 0 || top <= 0 || max_tiles <= 0 || max_tiles > 65535 || ldx < K) return LLMX_REFUSED(1);
+  if (x_dtype != w_dtype) return LLMX_REFUSED(2);
+  dim3 grid((N + MOE_TILE - 1) / MOE_TILE, max_tiles);
+#define GO(TX, TY, G)                                                                                          \
+  launch_pdl(moe_grouped_fma_kernel<TX, TX, TY, G>, grid, dim3(256), 0, stream, (const TX*)X, ldx, (const TX*)W, \
+             (TY*)Y, perm, tiles, pair_weight, top, n_tokens, N, K)
+  if (gated) {
+    if (x_dtype == LLMX_F32 && y_dtype == LLMX_F32) GO(float, float, true);
+    else if (x_dtype == LLMX_BF16 && y_dtype == LLMX_BF16) GO(bf16, bf16, true);
+    else return LLMX_REFUSED(2);
+  } else {
+    if (y_dtype != LLMX_F32) return LLMX_REFUSED(2);
+    if (x_dtype == LLMX_F32) GO(float, float, false);
+    else if (x_dtype == LLMX_BF16) GO(bf16, float, false);
+    else return LLMX_REFUSED(2);
+  }
+#undef GO
+  return LLMX_LAUNCH_STATUS();
+}

@@ -84,9 +84,10 @@ class DecoderModel:
                              else (probe(f"l_out-{i - 1}", t) if i else None))
             pending = self.blocks[call.layer].forward(h, pending, ctx, cache.view(call.cache), call.writes_cache)
         ctx.probe = probe
-        if probe and pending is not None:
-            kernels.add_rms_norm(h, pending, self.final_norm.gain, self.final_norm.eps, None)     # h += the last delta
-            pending = None
+        if probe:
+            if pending is not None:
+                kernels.add_rms_norm(h, pending, self.final_norm.gain, self.final_norm.eps, None)  # h += the last delta
+                pending = None
             probe(f"l_out-{len(self.spec.schedule) - 1}", h)
         n_want = ctx.want_rows.numel()
         if n_want == 0:

@@ -21,6 +21,7 @@ from pathlib import Path
 
 import numpy as np
 
+from ..cache import PAGE, pages_for
 from .engine import Engine, LoadOptions
 
 
@@ -68,13 +69,15 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time (the cache's pages are sized from it, with "
+                         "room for every live request's last, partly filled page)")
     ap.add_argument("--dump", action="store_true",
                     help="also write every step's named intermediates as <step>.<name>.f32")
     args = ap.parse_args(argv)
-    opts = LoadOptions(dtype=args.dtype, max_tokens=args.max_tokens,
-                       max_batch=max(1, (args.max_tokens + 63) // 64),
-                       max_step_tokens=max(args.max_tokens, 64))
+    # A request holds whole pages: beside the tokens themselves, up to one page per live request is padding.
+    max_batch = max(1, min(args.max_tokens, 256))
+    opts = LoadOptions(dtype=args.dtype, max_tokens=(pages_for(args.max_tokens) + max_batch) * PAGE,
+                       max_batch=max_batch, max_step_tokens=max(args.max_tokens, 64))
     engine = Engine.load(args.model, opts)
     rp = Replayer(engine, args.out, dump=args.dump)
     for line in sys.stdin:

@@ -289,7 +289,7 @@ def add_gain_sumsq(h: torch.Tensor, delta, gain: torch.Tensor, x_out: torch.Tens
 
 def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos, q_gain, k_gain,
                        eps: float, cos, sin, n_rot: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                       write_cache: bool = True) -> None:
+                       write_cache: bool = True, v_head_dim=None) -> None:
     """qkv [T,(H+2G)*D], or float32 split partials [S,T,(H+2G)*D] summed in
     order -> q_out [T,H*D] (normed, rotated) and, when ``write_cache``, k
     (normed, rotated) and v into the paged cache entry ``k_cache``/``v_cache``
@@ -300,18 +300,20 @@ def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, tok
     if qkv.dim() == 3:
         n_split, stride = qkv.shape[0], qkv.stride(0)
     T = qkv.shape[-2]
-    assert qkv.shape[-1] == (n_heads + 2 * n_kv_heads) * head_dim
+    v_head_dim = v_head_dim or head_dim          # values may have a size of their own (the row's last part)
+    assert qkv.shape[-1] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
+    assert q_out.shape[-1] == n_heads * head_dim
     assert k_cache.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
     if head_dim > 256 or head_dim % 2:
         raise Unsupported(f"head_dim {head_dim}: the q/k norm and rotation kernel takes even sizes up to 256")
     f = _fn("elementwise", "llmx_qk_norm_rope_cache",
             [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
              c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(qkv), _tag(qkv), n_split, stride, _ptr(q_out), _tag(q_out), _ptr(k_cache), _ptr(v_cache),
              _tag(k_cache), _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(token_pos),
              _ptr(q_gain), _ptr(k_gain), eps, _ptr(cos), _ptr(sin), n_rot, T, n_heads, n_kv_heads, head_dim,
-             int(write_cache), _stream()), "qk_norm_rope_cache")
+             v_head_dim, int(write_cache), _stream()), "qk_norm_rope_cache")
 
 
 def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
@@ -341,20 +343,23 @@ def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos, n_heads: int,
-                    n_kv_heads: int, head_dim: int, window, scale: float) -> None:
-    """General attention over the paged cache; q, out [T,H*D]."""
+                    n_kv_heads: int, head_dim: int, window, scale: float, v_head_dim=None, keep_first: int = 0) -> None:
+    """General attention over the paged cache; q [T,H*D] (rows may be the first columns of wider rows), out
+    [T,H*Dv].  Under a window the first ``keep_first`` keys of a sequence stay visible."""
     _dev(q, out, k_cache, v_cache, block_table, token_seq, token_pos)
-    _contig("q", q), _contig("out", out), _contig("block_table", block_table)
-    if head_dim > 256:
-        raise Unsupported(f"head_dim {head_dim}: the general attention kernel takes sizes up to 256")
+    _contig("out", out), _contig("block_table", block_table)
+    v_head_dim = v_head_dim or head_dim
+    assert q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim and out.shape[1] == n_heads * v_head_dim
+    if head_dim > 256 or v_head_dim > 256:
+        raise Unsupported(f"head_dim {head_dim}/{v_head_dim}: the general attention kernel takes sizes up to 256")
     if n_heads % n_kv_heads:
         raise Unsupported(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
     f = _fn("attention", "llmx_attention_paged",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _tag(q), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
              block_table.shape[1], _ptr(token_seq), _ptr(token_pos), q.shape[0], n_heads, n_kv_heads, head_dim,
-             int(window or 0), scale, _stream()), "attention_paged")
+             v_head_dim, q.stride(0), int(window or 0), int(keep_first or 0), scale, _stream()), "attention_paged")
 
 
 def n_sm(device=None) -> int:
@@ -606,3 +611,104 @@ def sample(logits, temperature, top_k, top_p, repeat_penalty, recent, uniform, o
     _check(f(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
              _ptr(top_p), _ptr(repeat_penalty), _ptr(recent), width, _ptr(uniform), _ptr(out_tokens),
              _ptr(status), _stream()), "sample")
+
+
+# ---- linear attention with a decay ---------------------------------------------------------------------
+
+_ACTS = {"none": 0, "silu": 1, "sigmoid": 2}
+
+
+def _split_view(proj):
+    """(n_split, split stride, row stride) of a product's output: [T, N], or float32 partials [S, T, N]."""
+    assert proj.stride(-1) == 1
+    if proj.dim() == 3:
+        return proj.shape[0], proj.stride(0), proj.stride(1)
+    return 1, 0, proj.stride(0)
+
+
+def decay_scan(proj, out, state, seq_start, seq_past, seq_slot, decay, cos, sin, n_rot: int, activation: str,
+               k_scale: float, n_heads: int, head_dim: int, v_head_dim: int, q_off: int, k_off: int, v_off: int) -> None:
+    """The recurrence S = decay_h S + k v^T, o = S^T q over every sequence's tokens of the step, in order.
+    ``proj`` [T, N] (or split partials [S, T, N]) holds q heads at column ``q_off``, k heads at ``k_off``
+    (``head_dim`` each) and v heads at ``v_off`` (``v_head_dim`` each); ``activation`` is applied to all three,
+    then q and k are rotated (first ``n_rot`` dims, float32 tables) and k is scaled.  ``out`` float32
+    [T, H*Dv]; ``state`` float32 [slots, H, D, Dv], read and written in place for the step's slots."""
+    _dev(proj, out, state, seq_start, seq_past, seq_slot, decay, cos, sin)
+    _contig("out", out), _contig("state", state)
+    assert out.dtype == torch.float32 and state.dtype == torch.float32 and decay.dtype == torch.float32
+    assert state.shape[1:] == (n_heads, head_dim, v_head_dim) and decay.numel() == n_heads
+    n_split, split_stride, row_stride = _split_view(proj)
+    n_seqs = seq_past.numel()
+    f = _fn("linear_attention", "llmx_decay_scan",
+            [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), _tag(proj), n_split, split_stride, row_stride, q_off, k_off, v_off, _ptr(out), _ptr(state),
+             _ptr(seq_start), _ptr(seq_past), _ptr(seq_slot), _ptr(decay), _ptr(cos), _ptr(sin), n_rot,
+             _ACTS[activation], k_scale, n_seqs, n_heads, head_dim, v_head_dim, n_sm(out.device), _stream()),
+           "decay_scan")
+
+
+def gated_norm(o, proj, g_off: int, gain, eps: float, gate: str, per_head: bool, y, n_heads: int,
+               v_head_dim: int) -> None:
+    """y = o / sqrt(mean(o^2) + eps) * gain * gate(proj[:, g_off:]) with the mean over one head's columns
+    (``per_head``) or over the whole row; o float32 [T, H*Dv]; ``gain`` float32 [H*Dv] or None."""
+    _dev(o, proj, gain, y)
+    _contig("o", o), _contig("y", y)
+    assert o.dtype == torch.float32 and y.shape == o.shape and (gain is None or gain.dtype == torch.float32)
+    n_split, split_stride, row_stride = _split_view(proj)
+    f = _fn("linear_attention", "llmx_gated_norm",
+            [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_float, c_int, c_int, c_void_p,
+             c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(o), _ptr(proj), _tag(proj), n_split, split_stride, row_stride, g_off, _ptr(gain), eps, _ACTS[gate],
+             int(per_head), _ptr(y), _tag(y), o.shape[0], n_heads, v_head_dim, _stream()), "gated_norm")
+
+
+# ---- routed experts ------------------------------------------------------------------------------------
+
+MOE_TILE = 64          # rows per tile of the grouped products; the same constant as in moe.cu
+_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_route(logits, ids, weights, top: int, n_groups: int, keep_groups: int, group_top: int, score: str,
+              normalize: bool, norm_eps: float, scale: float) -> None:
+    """Per token (row of float32 ``logits`` [T, E]): its ``top`` experts (``ids`` int32 [T, top]) and their
+    weights (float32 [T, top]); see moe.cu for the rule."""
+    _dev(logits, ids, weights)
+    _contig("logits", logits), _contig("ids", ids), _contig("weights", weights)
+    assert logits.dtype == torch.float32 and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    T, E = logits.shape
+    f = _fn("moe", "llmx_moe_route",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+             c_void_p])
+    _check(f(_ptr(logits), _ptr(ids), _ptr(weights), T, E, top, n_groups, keep_groups, group_top, _SCORES[score],
+             int(normalize), norm_eps, scale, _stream()), "moe_route")
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+    return (n_pairs + MOE_TILE - 1) // MOE_TILE + n_experts
+
+
+def moe_sort(ids, n_experts: int, perm, tiles) -> None:
+    """Orders the (token, choice) pairs by expert: ``perm`` int32 [P] (sorted place -> pair) and ``tiles``
+    int32 [max_tiles, 3] (expert or -1, first row, rows)."""
+    _dev(ids, perm, tiles)
+    _contig("ids", ids), _contig("perm", perm), _contig("tiles", tiles)
+    f = _fn("moe", "llmx_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(ids), ids.numel(), n_experts, _ptr(perm), _ptr(tiles), tiles.shape[0], _stream()), "moe_sort")
+
+
+def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gated: bool) -> None:
+    """Grouped products over the sorted pairs.  ``gated``: x [T, K] gathered through ``perm``, w [E, 2F, K]
+    (gate rows, then up rows), y [P, F] = silu(gate) * up in sorted order.  Else: x [P, K] in sorted order,
+    w [E, N, K], y float32 [top, T, N] = weight of the pair times the product."""
+    _dev(x, w, y, perm, tiles, pair_weight)
+    _contig("w", w), _contig("y", y)
+    assert x.stride(1) == 1 and x.dtype == w.dtype
+    K = x.shape[1]
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    assert w.shape[2] == K
+    f = _fn("moe", "llmx_moe_grouped_fma",
+            [c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(w), _tag(w), _ptr(y), _tag(y), _ptr(perm), _ptr(tiles), tiles.shape[0],
+             _ptr(pair_weight), top, n_tokens, N, K, int(gated), _stream()), "moe_grouped")

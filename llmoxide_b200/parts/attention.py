@@ -8,6 +8,14 @@ v untouched; k and v of the whole step are stored before any score is taken;
 query head hq reads kv head hq // (H/G); scores are scaled by ``scale``; the
 query at position p sees keys first..p, first = 0 or p-(w-1) under a window
 (crates/model/src/cache.rs:31-37).
+
+Beyond the reference's layer: values may have a size of their own
+(``v_head_dim``); under a window the first ``keep_first`` keys of a sequence
+may stay visible (a position sees key j if j <= p and (p - j < window or
+j < keep_first)); a layer without key/value projections of its own
+(``own_kv`` false) only makes queries and reads the cache entry of the call
+that owns it, which then keeps what the widest of its readers can see
+(``cache_window``, ``cache_keep_first``).
 """
 
 from __future__ import annotations
@@ -27,21 +35,34 @@ class GQAttention:
         self.rt = rt
         self.H, self.G, self.D = spec["n_heads"], spec["n_kv_heads"], spec["head_dim"]
         self.scale = float(spec["scale"])
+        self.Dv = spec.get("v_head_dim") or self.D
         self.window = spec.get("window")
+        self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
+        # what the cache entry holds: this layer's own mask unless the description names a wider one
+        self.cache_window = spec.get("cache_window", self.window) if "cache_window" in spec.params else self.window
+        self.cache_keep_first = int(spec.get("cache_keep_first", self.keep_first) or 0) if self.cache_window else 0
+        self.own_kv = bool(spec.get("own_kv", True))
         self.eps = float(spec.get("qk_norm_eps") or 0.0)
         if self.H % self.G:
             raise Unsupported(f"{self.H} heads are not a multiple of {self.G} kv heads")
-        if self.D % 16 or self.D > 256:
+        self.plain = self.Dv == self.D and not self.keep_first      # the shape the tiled kernels are written for
+        if self.plain and (self.D % 16 or self.D > 256):
             raise Unsupported(f"head_dim {self.D}: the attention kernels take multiples of 16 up to 256")
+        if max(self.D, self.Dv) > 256:
+            raise Unsupported(f"head sizes {self.D}/{self.Dv}: the attention kernels take sizes up to 256")
         t = spec.tensors
-        wq, wk, wv = (weights.pop(t[r].name) for r in ("q", "k", "v"))
-        if not (wq.dtype == wk.dtype == wv.dtype):
-            wq, wk, wv = wq.float(), wk.float(), wv.float()
-        # One matrix product for q, k and v: rows of q, then k, then v.
-        wqkv = torch.cat([wq, wk, wv], dim=0)
-        del wq, wk, wv
-        self.qkv = Linear(wqkv, rt)
-        self.q_only = Linear(wqkv[: self.H * self.D], rt)
+        if self.own_kv:
+            wq, wk, wv = (weights.pop(t[r].name) for r in ("q", "k", "v"))
+            if not (wq.dtype == wk.dtype == wv.dtype):
+                wq, wk, wv = wq.float(), wk.float(), wv.float()
+            # One matrix product for q, k and v: rows of q, then k, then v.
+            wqkv = torch.cat([wq, wk, wv], dim=0)
+            del wq, wk, wv
+            self.qkv = Linear(wqkv, rt)
+            self.q_only = Linear(wqkv[: self.H * self.D], rt)
+        else:
+            self.qkv = None
+            self.q_only = Linear(weights.pop(t["q"].name), rt)
         self.o = Linear(weights.pop(t["o"].name), rt)
         self.q_gain = self.k_gain = None
         if "q_norm" in t:
@@ -50,15 +71,18 @@ class GQAttention:
         self.position = position
 
     def cache_need(self):
-        return KVNeed(self.G, self.D, self.window), None
+        return KVNeed(self.G, self.D, self.cache_window, v_head_dim=None if self.Dv == self.D else self.Dv,
+                      keep_first=self.cache_keep_first), None
 
     @property
     def takes_row_scales(self) -> bool:
         """Its first products (q|k|v) can apply a norm's row scales in their epilogue."""
-        return self.qkv.takes_row_scales and self.q_only.takes_row_scales
+        return (self.qkv is None or self.qkv.takes_row_scales) and self.q_only.takes_row_scales
 
     def libraries(self) -> set:
-        libs = {"elementwise"} | self.qkv.libraries() | self.o.libraries()
+        libs = {"elementwise"} | self.q_only.libraries() | self.o.libraries()
+        if not self.plain:
+            return libs | {"attention"}
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
             libs |= {"attention_decode",
                      "attention_prefill_tc" if self.D == 128 else "attention_prefill" if self.D == 64 else "attention"}
@@ -69,23 +93,29 @@ class GQAttention:
     adds_to_residual = True      # forward() takes ``residual`` and may return None: "already added"
 
     def forward(self, x, ctx, view, writes_cache=True, residual=None):
-        H, G, D = self.H, self.G, self.D
+        H, G, D, Dv = self.H, self.G, self.D, self.Dv
         T = x.shape[0]
         dev = x.device
         tables = self.position.rotary_tables() if self.position is not None else None
         cos, sin, n_rot = tables if tables is not None else (None, None, 0)
         block_table = ctx.block_tables[view.group]
-        if writes_cache:
-            qkv = self.qkv(x, splits_ok=True)
+        if writes_cache and not self.own_kv:
+            raise Unsupported("a layer without key/value projections cannot write a cache entry")
+        if not writes_cache and self.q_gain is None and n_rot == 0:
+            # A call that reads another call's cache entry makes only queries; nothing is done to them.
+            q = self.q_only(x, out_dtype=self.rt.act_dtype)
         else:
-            # A call that reads another call's cache entry makes only queries.
-            q_part = self.q_only(x)
-            qkv = torch.empty((T, (H + 2 * G) * D), dtype=q_part.dtype, device=dev)
-            qkv[:, : H * D] = q_part
-        q = torch.empty((T, H * D), dtype=self.rt.act_dtype, device=dev)
-        kernels.qk_norm_rope_cache(qkv, q, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
-                                   self.q_gain, self.k_gain, self.eps, cos, sin, n_rot, H, G, D, writes_cache)
-        out = torch.empty_like(q)
+            if writes_cache:
+                qkv = self.qkv(x, splits_ok=True)
+            else:
+                q_part = self.q_only(x)
+                qkv = torch.empty((T, (H + G) * D + G * Dv), dtype=q_part.dtype, device=dev)
+                qkv[:, : H * D] = q_part
+            q = torch.empty((T, H * D), dtype=self.rt.act_dtype, device=dev)
+            kernels.qk_norm_rope_cache(qkv, q, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
+                                       self.q_gain, self.k_gain, self.eps, cos, sin, n_rot, H, G, D, writes_cache,
+                                       v_head_dim=Dv)
+        out = torch.empty((T, H * Dv), dtype=self.rt.act_dtype, device=dev)
         self.attend(q, out, view, block_table, ctx)
         if residual is not None and self.o.add_into(out, residual):
             return None
@@ -97,7 +127,8 @@ class GQAttention:
         kernel at head size 64; the general kernel otherwise and always in
         float32."""
         H, G, D = self.H, self.G, self.D
-        fast = q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16 and self.rt.tensor_cores
+        fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
+                and self.rt.tensor_cores)
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
                                      self.scale)
@@ -109,4 +140,4 @@ class GQAttention:
                                       ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale)
         else:
             kernels.attention_paged(q, out, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
-                                    H, G, D, self.window, self.scale)
+                                    H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first)

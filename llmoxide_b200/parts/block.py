@@ -5,7 +5,8 @@ h += mixer(norm(h)); h += feed_forward(norm(h)).
 
 The residual stream stays float32.  Each residual add is fused into the norm
 that follows it, so a block hands its last delta on as ``pending`` instead of
-adding it itself.  A mixer or feed-forward with ``adds_to_residual`` is given the
+adding it itself.  ``parallel`` is the block with one norm whose output both
+sublayers read: h += mixer(norm(h)) + feed_forward(norm(h)).  A mixer or feed-forward with ``adds_to_residual`` is given the
 stream (``residual=h``) and may add its result there itself, in the kernel of its
 last product; it then returns None, and the norm that follows has nothing to add."""
 
@@ -92,3 +93,47 @@ def rt_shared_position(spec, weights, rt):
 
 def build_block(spec, weights: dict, rt):
     return lookup(ARRANGEMENTS, "block arrangement", spec.arrangement)(spec, weights, rt)
+
+
+@register_arrangement("parallel")
+class ParallelBlock:
+    """One norm, and both sublayers read its output: x = norm(h); h += mixer(x) + feed_forward(x).  The mixer's
+    result joins the float32 stream at once (nothing else reads the stream before the next layer's norm, and the
+    feed-forward reads x); the feed-forward's is handed on as the pending delta, which the next norm adds."""
+
+    def __init__(self, spec, weights: dict, rt):
+        position = None
+        if spec.position is not None:
+            position = rt_shared_position(spec.position, weights, rt)
+        self.norm = build_part(NORMS, "norm", spec.norms["shared"], weights, rt)
+        self.mixer = lookup(MIXERS, "mixer", spec.mixer.kind)(spec.mixer, position, weights, rt)
+        self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", spec.feed_forward, weights, rt)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def libraries(self) -> set:
+        libs = set()
+        for part in (self.norm, self.mixer, self.feed_forward):
+            libs |= getattr(part, "libraries", set)()
+        return libs
+
+    def forward(self, h, pending, ctx, view, writes_cache=True):
+        probe = getattr(ctx, "probe", None)
+        x = self.norm.add_forward(h, pending)
+        if probe:
+            probe("resid_in", h), probe("attn_norm", x)
+        if probe is None and getattr(self.mixer, "adds_to_residual", False):
+            a = self.mixer.forward(x, ctx, view, writes_cache, residual=h)
+        else:
+            a = self.mixer.forward(x, ctx, view, writes_cache)
+        if probe:
+            probe("attn_output", _summed(a))
+        out = self.feed_forward.forward(x, ctx)
+        if probe and out is not None:
+            probe("ffn_out", _summed(out))
+        if a is not None:
+            if out is None:
+                return a
+            kernels.add_rms_norm(h, a, self.norm.gain, self.norm.eps, None)      # h += a; nothing is normed
+        return out

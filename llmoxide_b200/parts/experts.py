@@ -1,0 +1,87 @@
+"""Routed experts as a feed-forward: every token uses ``top`` of ``n_experts``
+small gated layers, down(act(gate x) * (up x)), weighted by the router.
+
+Router logits z = W_r x are float32 (the router's matrix is kept in float32;
+x may be the compute dtype's rounding).  Scores are sigmoids of z (or a
+softmax over z).  With ``n_groups`` > 1 the experts form equal groups of
+neighbours, a group scores the sum of its ``group_score_top`` largest scores,
+and only experts of the ``keep_groups`` best groups can be chosen.  The
+chosen experts' scores, divided by their sum + ``normalize_eps`` when
+``normalize``, times ``scale``, weight the experts' outputs.
+
+The step's (token, choice) pairs are ordered by expert on the device and the
+two products run grouped over that order (csrc/moe.cu), so nothing is read
+back to the host and a decode step stays inside a CUDA graph.  The result is
+handed on as one float32 partial per choice, [top, T, d], which the norm that
+adds it to the residual stream sums in order.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..errors import ConfigError, Unsupported
+from .linear import Linear
+from .registry import register_feed_forward
+
+
+@register_feed_forward("none")
+class NoFeedForward:
+    """A layer without a feed-forward."""
+
+    def __init__(self, spec, weights: dict, rt):
+        pass
+
+    def libraries(self) -> set:
+        return set()
+
+    def forward(self, x, ctx, residual=None):
+        return None
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts:
+    def __init__(self, spec, weights: dict, rt):
+        if spec.get("activation", "silu") != "silu":
+            raise Unsupported(f"routed_experts activation {spec.get('activation')!r}: only 'silu' is built")
+        self.rt = rt
+        self.E, self.top, self.F = spec["n_experts"], spec["top"], spec["intermediate_size"]
+        self.n_groups, self.keep_groups = spec.get("n_groups", 1), spec.get("keep_groups", 1)
+        self.group_top = spec.get("group_score_top", 2)
+        self.score = spec.get("score", "sigmoid")
+        self.normalize, self.norm_eps = bool(spec.get("normalize", True)), float(spec.get("normalize_eps", 0.0))
+        self.scale = float(spec.get("scale", 1.0))
+        if self.E % self.n_groups or self.top > self.E // self.n_groups * self.keep_groups:
+            raise ConfigError(f"{self.E} experts in {self.n_groups} groups, {self.keep_groups} kept, top {self.top}")
+        if self.E > 1024 or self.top > 16:
+            raise Unsupported(f"{self.E} experts / top {self.top}: the routing kernel takes up to 1024 / 16")
+        t = spec.tensors
+        # the router decides in float32 whatever the compute dtype
+        self.router = Linear(weights.pop(t["router"].name).to(torch.float32).contiguous(), rt)
+        dt = rt.act_dtype
+        gate_up = [torch.cat([weights.pop(t[f"gate{e}"].name), weights.pop(t[f"up{e}"].name)], dim=0).to(dt)
+                   for e in range(self.E)]
+        self.gate_up = torch.stack(gate_up).contiguous()             # [E, 2F, d]: gate rows, then up rows
+        del gate_up
+        self.down = torch.stack([weights.pop(t[f"down{e}"].name).to(dt) for e in range(self.E)]).contiguous()  # [E, d, F]
+
+    def libraries(self) -> set:
+        return {"moe"} | self.router.libraries()
+
+    def forward(self, x, ctx, residual=None):
+        T, dev = x.shape[0], x.device
+        P = T * self.top
+        logits = self.router(x, out_dtype=torch.float32)
+        ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
+        pair_w = torch.empty((T, self.top), dtype=torch.float32, device=dev)
+        kernels.moe_route(logits, ids, pair_w, self.top, self.n_groups, self.keep_groups, self.group_top, self.score,
+                          self.normalize, self.norm_eps, self.scale)
+        perm = torch.empty((P,), dtype=torch.int32, device=dev)
+        tiles = torch.empty((kernels.moe_max_tiles(P, self.E), 3), dtype=torch.int32, device=dev)
+        kernels.moe_sort(ids, self.E, perm, tiles)
+        act = torch.empty((P, self.F), dtype=self.rt.act_dtype, device=dev)
+        kernels.moe_grouped(x, self.gate_up, act, perm, tiles, pair_w, self.top, T, gated=True)
+        y = torch.empty((self.top, T, self.down.shape[1]), dtype=torch.float32, device=dev)
+        kernels.moe_grouped(act, self.down, y, perm, tiles, pair_w, self.top, T, gated=False)
+        return y

@@ -2,8 +2,10 @@
 first n_rot dims of a head by angle pos * base^(-2i/n_rot).  The angle is a
 float64 recurrence theta_{i+1} = theta_i * base^(-2/n_rot) starting at pos,
 and only sin/cos are rounded to float32, as the reference computes it
-(crates/model/src/ops.rs:142-159, base held as float32).  ``none`` rotates
-nothing."""
+(crates/model/src/ops.rs:142-159, base held as float32).  With
+``angles="float32"`` the angle itself is a float32 product of the position and
+the float32 frequency base^(-2i/n_rot), for designs that compute positions and
+angles in 32-bit.  ``none`` rotates nothing."""
 
 from __future__ import annotations
 
@@ -18,6 +20,7 @@ class RotaryNeox:
     def __init__(self, spec, weights: dict, rt):
         self.n_rot, self.base, self.rt = int(spec["n_rot"]), float(spec["base"]), rt
         self.factors = spec.get("factors")  # optional per-pair divisors of the angle
+        self.angles = spec.get("angles", "float64")
         if self.n_rot % 2:
             raise ValueError(f"n_rot {self.n_rot} must be even")
         self._tables = None
@@ -31,6 +34,12 @@ class RotaryNeox:
             cos = np.empty((n, half), dtype=np.float32)
             sin = np.empty((n, half), dtype=np.float32)
             for i in range(half):
+                if self.angles == "float32":
+                    freq = np.float32(self.base ** (-2.0 * i / self.n_rot))
+                    angle = (np.arange(n, dtype=np.float32) * freq).astype(np.float64)
+                    cos[:, i] = np.cos(angle).astype(np.float32)
+                    sin[:, i] = np.sin(angle).astype(np.float32)
+                    continue
                 angle = theta if self.factors is None else theta / float(np.float32(self.factors[i]))
                 cos[:, i] = np.cos(angle).astype(np.float32)
                 sin[:, i] = np.sin(angle).astype(np.float32)
