@@ -5,6 +5,7 @@ B200.  A "step" is one decode step of a batch of 8 sequences from depth 2048
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
     python bench.py --cpu-baseline      # the plain implementation of tests/ on the CPU, tiny configurations
+    python bench.py --design tifapel    # the Tifapel decoder beside the dense decoder at equal layer sizes
 
 ``value`` is device-timed (CUDA events around K steps queued back to back);
 ``e2e`` is the same metric through ``Session.generate`` with host token ids in
@@ -193,6 +194,10 @@ def main() -> int:
                          "one replayed decode step, when each kernel's dependency resolved")
     ap.add_argument("--cpu-baseline", action="store_true",
                     help="instead of the benchmark: time the plain implementation of tests/ on the CPU (tiny configurations)")
+    ap.add_argument("--design", choices=["tifapel"], default=None,
+                    help="instead of the benchmark: prefill and decode rates of that design at layer sizes of a real "
+                         "model (random weights), beside the dense Qwen3 decoder at equal sizes, with every kernel's "
+                         "time per step (one JSON line of its own; the default workload is untouched)")
     ap.add_argument("--cuda-profiler", choices=["decode", "prefill"], default=None,
                     help="bracket that region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -204,6 +209,8 @@ def main() -> int:
         return 0
     if args.cpu_baseline:
         return cpu_baseline()
+    if args.design:
+        return design_bench(args)
     if args.gpus != 1:
         print(json.dumps({"note": f"this library runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
         return 2
@@ -380,6 +387,153 @@ def main() -> int:
         points=points, point_details=details, e2e=e2e, gpu_launches=launches, clocks=clocks,
     )
     print(json.dumps(line))
+    return 0
+
+
+# ---- another design beside the dense decoder ------------------------------------------------------------------
+
+def tifapel_layers(n_layers, width, heads, kv_heads, dim, window, keep, experts, top, ff, groups):
+    """Layers in the order attention, lightning, retention, attention reading the first one's keys and values."""
+    moe = dict(kind="moe", expert=dict(ff=ff),
+               router=dict(experts=experts, top=top, scale=1.0, groups=dict(count=groups[0], keep=groups[1])))
+    decay = [1.0 - 2.0 ** -(3 + 7 * h / max(1, heads - 1)) for h in range(heads)]
+    att = dict(type="attention", mlp=moe, mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim,
+                                                     scale=dim ** -0.5, mask=dict(size=window, keep_first=keep)))
+    out = []
+    for i in range(n_layers):
+        kind = i % 4
+        if kind == 0:
+            out.append(json.loads(json.dumps(att)))
+        elif kind == 1:
+            out.append(dict(type="lightning", mlp=moe, mixer=dict(heads=heads, dim=dim, vdim=dim, decay=decay)))
+        elif kind == 2:
+            out.append(dict(type="retention", mlp=moe, mixer=dict(heads=heads, dim=dim, vdim=dim, decay=decay,
+                                                                  rot=dict(dims=dim, base=1000000.0))))
+        else:
+            layer = json.loads(json.dumps(att))
+            layer["mixer"]["kv_from"] = i - 3
+            out.append(layer)
+    return out
+
+
+def design_bench(args) -> int:
+    """Prefill and decode rates of the Tifapel decoder at layer sizes that resemble a real model's (width 2048,
+    16 heads of 128 on 4 key/value heads, a window of 1024 that keeps 4 tokens, 16 experts of 1024 of which a
+    token uses 2 from 2 of 4 groups), beside the dense Qwen3 decoder with the same width, heads and layer count and
+    a feed-forward as wide as a token's two experts.  Device-timed with CUDA events, median of 5; weights and
+    cache are larger than L2.  Then one prompt step and one decode step of each model with every kernel between
+    two events of its own (no launch overlaps another), summed by kernel."""
+    import numpy as np
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    from llmoxide_b200 import Engine, LoadOptions, kernels, read_config
+
+    L = min(args.layers, 8) if args.layers != QWEN3_8B["num_hidden_layers"] else 8
+    width, heads, kv, dim, window, keep, E, top, ff = 2048, 16, 4, 128, 1024, 4, 16, 2, 1024
+    vocab = 32768
+    T, B, depth = args.prefill_tokens, args.batch, args.depth
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(0)
+    models = {
+        "tifapel": dict(architecture="Tifapel", vocab=vocab, width=width, norm=dict(eps=1e-6),
+                        layers=tifapel_layers(L, width, heads, kv, dim, window, keep, E, top, ff, (4, 2))),
+        "dense": dict(QWEN3_8B, num_hidden_layers=L, hidden_size=width, num_attention_heads=heads,
+                      num_key_value_heads=kv, head_dim=dim, intermediate_size=top * ff, vocab_size=vocab,
+                      use_sliding_window=True, sliding_window=window, max_window_layers=0, eos_token_id=0),
+    }
+
+    def event_ms(fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    def per_kernel(eng, entries):
+        """One eager step with every launch between two events; {kernel: (launches, ms)}."""
+        records, raw_fn = [], kernels._fn
+
+        def timed_fn(lib, name, argtypes):
+            f = raw_fn(lib, name, argtypes)
+
+            def call(*a):
+                tag = name.replace("llmx_", "")
+                if name.startswith("llmx_gemm_tc"):
+                    tag += f" N{a[5]} K{a[6]}"
+                elif name == "llmx_gemm_fma":
+                    tag += f" N{a[7]} K{a[8]}"
+                elif name == "llmx_moe_grouped_tc":
+                    tag += " gate|up" if a[15] else " down"
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                code = f(*a)
+                e1.record()
+                records.append((tag, e0, e1))
+                return code
+            return call
+
+        kernels._fn = timed_fn
+        kernels.set_overlap(False)
+        graphs, eng.options.cuda_graphs = eng.options.cuda_graphs, False
+        try:
+            eng.step(entries)
+            torch.cuda.synchronize()
+        finally:
+            kernels._fn = raw_fn
+            kernels.set_overlap(True)
+            eng.options.cuda_graphs = graphs
+        out = {}
+        for tag, e0, e1 in records:
+            n, ms = out.get(tag, (0, 0.0))
+            out[tag] = (n + 1, ms + e0.elapsed_time(e1))
+        return {k: dict(launches=n, ms=round(ms, 4)) for k, (n, ms) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+    result = {}
+    for name, raw in models.items():
+        cfg = read_config(raw)
+        eng = Engine.random(cfg, seed=0, options=LoadOptions(dtype="bfloat16", max_tokens=(B + 1) * (depth + 512) + T,
+                                                             max_batch=B + 1, max_step_tokens=max(T, depth)))
+        torch.cuda.synchronize()
+        print(f"[bench] {name}: {cfg.summary()}", file=sys.stderr)
+
+        def prefill_once():
+            s = eng.acquire()
+            eng.step([(s, rng.integers(0, vocab, T).tolist())])
+            eng.release(s)
+
+        for _ in range(3):
+            prefill_once()
+        pre_ms = statistics.median(event_ms(prefill_once) for _ in range(5))
+        s = eng.acquire()
+        pre_kernels = per_kernel(eng, [(s, rng.integers(0, vocab, T).tolist())])
+        eng.release(s)
+        slots = [eng.acquire() for _ in range(B)]
+        for sl in slots:
+            eng.step([(sl, rng.integers(0, vocab, depth).tolist())], [[]])
+        K, W = args.steps, max(args.warmup, 3)
+        toks = rng.integers(0, vocab, (W + K + 1, B)).tolist()
+        for i in range(W):
+            eng.step([(sl, [t]) for sl, t in zip(slots, toks[i])])
+        launches = kernels.launch_count
+        dec_ms = event_ms(lambda: [eng.step([(sl, [t]) for sl, t in zip(slots, toks[i])]) for i in range(W, W + K)]) / K
+        launches = (kernels.launch_count - launches) // K
+        dec_kernels = per_kernel(eng, [(sl, [t]) for sl, t in zip(slots, toks[W + K])])
+        eng.check_status()
+        result[name] = dict(prefill_tokens=T, prefill_ms=round(pre_ms, 3), prefill_tokens_per_s=round(T / pre_ms * 1e3),
+                            decode_batch=B, decode_depth=depth, decode_ms_per_step=round(dec_ms, 4),
+                            decode_tokens_per_s=round(B / dec_ms * 1e3), launches_per_decode_step=launches,
+                            prefill_kernels=pre_kernels, decode_kernels=dec_kernels)
+        print(f"[bench] {name}: prefill {T} tokens {pre_ms:.2f} ms, decode b{B} {dec_ms:.3f} ms/step", file=sys.stderr)
+        del eng
+        torch.cuda.empty_cache()
+    print(json.dumps(dict(design="tifapel", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src,
+                          hbm_gbs=pk["hbm_gbs"], bf16_tflops=pk["bf16_tflops"],
+                          sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, window=window, keep_first=keep,
+                                     experts=E, top=top, expert_ff=ff, dense_ff=top * ff, vocab=vocab),
+                          data="synthetic: seeded uniform token ids, random weights", **result)))
     return 0
 
 

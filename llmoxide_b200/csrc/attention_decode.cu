@@ -120,7 +120,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_past,
                         float* __restrict__ ws, unsigned int* __restrict__ counters, bf16* __restrict__ out, int H,
-                        int G, int window, float scale_log2, int n_chunks, int cluster_merge) {
+                        int G, int window, int keep_first, float scale_log2, int n_chunks, int cluster_merge) {
   using S = DecSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr uint32_t TILE_BYTES = 2u * DEC_TILE * D * 2u;        // what one stage's copies bring
@@ -157,17 +157,22 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   }
   __syncwarp();
 
-  // this warp's tiles of 32 keys: an equal share of the sequence's visible tiles
+  // this warp's tiles of 32 keys: an equal share of the sequence's visible tiles.  Under a window that keeps
+  // the sequence's first keys, the tiles that hold those and lie wholly before the window's first tile come
+  // first in the walk: place v of the walk is tile v, or past them tile t_first + (v - n_kept).
   const int t_first = first / DEC_TILE, t_last = p / DEC_TILE;
-  const int per_warp = (t_last - t_first + n_chunks * DEC_WARPS) / (n_chunks * DEC_WARPS);   // ceil(tiles / warps)
-  const int tile_lo = t_first + (chunk * DEC_WARPS + warp) * per_warp;
-  const int tile_hi = min(tile_lo + per_warp - 1, t_last);
+  const int n_kept = keep_first > 0 ? min(t_first, (keep_first + DEC_TILE - 1) / DEC_TILE) : 0;
+  const int n_walk = n_kept + t_last - t_first + 1;
+  const int per_warp = (n_walk - 1 + n_chunks * DEC_WARPS) / (n_chunks * DEC_WARPS);         // ceil(tiles / warps)
+  const int tile_lo = (chunk * DEC_WARPS + warp) * per_warp;                                // places of the walk
+  const int tile_hi = min(tile_lo + per_warp - 1, n_walk - 1);
   const int n_tiles = misaligned ? 0 : tile_hi - tile_lo + 1;     // <= 0: nothing to do
+  auto tile_at = [&](int v) { return v < n_kept ? v : t_first + (v - n_kept); };
 
   const bool withhold = llmx_withhold != 0;       // tests: the first CTA's first warp never asks for its first tile
-  auto load_tile = [&](int tile, int stage) {
-    if (withhold && tile == tile_lo && warp == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) return;
-    const int key0 = tile * DEC_TILE;
+  auto load_tile = [&](int place, int stage) {
+    if (withhold && place == tile_lo && warp == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) return;
+    const int key0 = tile_at(place) * DEC_TILE;
     const int phys = pages[key0 / LLMX_PAGE];
     const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE, bar = bars + 8 * stage;
     if (S::TMA) {
@@ -199,7 +204,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
   // Tiles before the new token's own are complete since earlier steps: they start now.
   int issued = 0;
-  for (; issued < DEC_STAGES - 1 && issued < n_tiles && tile_lo + issued < t_last; ++issued)
+  for (; issued < DEC_STAGES - 1 && issued < n_tiles && tile_at(tile_lo + issued) < t_last; ++issued)
     load_tile(tile_lo + issued, issued);
   pdl_wait();
 
@@ -227,7 +232,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * stage, (t / DEC_STAGES) & 1));   // the warp leaves together
       if (!ok) break;
       const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE;
-      const int key0 = (tile_lo + t) * DEC_TILE;
+      const int key0 = tile_at(tile_lo + t) * DEC_TILE;
       if (key0 + DEC_TILE - 1 > p) {
         // rows past the newest key were never written by this sequence: weight 0, but 0 * NaN is NaN
         uint8_t* vt = wsm + stage * 2 * S::TILE + S::TILE;
@@ -260,7 +265,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
         for (int e = 0; e < 2; ++e) {                              // rows gq and gq + 8
           const int key = key0 + 16 * i + gq + 8 * e;
-          const bool vis = key >= first && key <= p;
+          const bool vis = (key >= first || key < keep_first) && key <= p;
           s[i][2 * e] = vis ? s[i][2 * e] * scale_log2 : -INFINITY;
           s[i][2 * e + 1] = vis ? s[i][2 * e + 1] * scale_log2 : -INFINITY;
           mx0 = fmaxf(mx0, s[i][2 * e]);
@@ -505,7 +510,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 template <int D>
 static int launch_decode(const void* q, void* out, const void* k_cache, const void* v_cache, long long n_pages,
                          const int* block_table, int table_width, const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
-                         int window, float scale, int n_chunks, cudaStream_t stream) {
+                         int window, int keep_first, float scale, int n_chunks, cudaStream_t stream) {
   const int R = H / G;
   const int head_groups = (R + DEC_ROWS - 1) / DEC_ROWS;
   dim3 grid(n_chunks, G * head_groups, B);
@@ -533,11 +538,11 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
   if (cluster_merge)
     launch_pdl_cluster(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, (unsigned)n_chunks, mk, mv, (const bf16*)q,
                        (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters,
-                       (bf16*)out, H, G, window, scale * 1.4426950408889634f, n_chunks, cluster_merge);
+                       (bf16*)out, H, G, window, keep_first, scale * 1.4426950408889634f, n_chunks, cluster_merge);
   else
     launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, mk, mv, (const bf16*)q, (const bf16*)k_cache,
                (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters, (bf16*)out, H, G, window,
-               scale * 1.4426950408889634f, n_chunks, cluster_merge);
+               keep_first, scale * 1.4426950408889634f, n_chunks, cluster_merge);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -546,12 +551,14 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
 // Every sequence's visible keys are cut into n_chunks <= 32 shares.  With n_chunks > 8: ws is a float32 workspace
 // of B*H*n_chunks*(D+4) elements (16-byte aligned), and counters holds B * G * ceil((H/G)/8) words that are zero before the first
 // launch (each launch leaves them zero).
-LLMX_API int llmx_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                   long long n_pages, const int* block_table, int table_width, const int* seq_past, float* ws,
-                                   unsigned int* counters, int B, int H, int G, int D, int window, float scale,
-                                   int n_chunks, cudaStream_t stream) {
+// keep_first: under a window, the sequence's first keep_first keys stay visible.
+LLMX_API int llmx_attention_decode_keep(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                        long long n_pages, const int* block_table, int table_width, const int* seq_past,
+                                        float* ws, unsigned int* counters, int B, int H, int G, int D, int window,
+                                        int keep_first, float scale, int n_chunks, cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || window < 0 || n_chunks < 1 || n_chunks > DEC_MAX_CHUNKS ||
+  if (window <= 0) keep_first = 0;
+  if (H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || n_chunks < 1 || n_chunks > DEC_MAX_CHUNKS ||
       (n_chunks > 8 && (!ws || !counters || ((uintptr_t)ws & 15))) || n_pages <= 0 ||
       ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)q & 3))
     return LLMX_REFUSED(1);
@@ -559,7 +566,7 @@ LLMX_API int llmx_attention_decode(const void* q, void* out, const void* k_cache
 #define CASE(DD)                                                                                               \
   case DD:                                                                                                     \
     return launch_decode<DD>(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, \
-                             B, H, G, window, scale, n_chunks, stream)
+                             B, H, G, window, keep_first, scale, n_chunks, stream)
   switch (D) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
     CASE(144); CASE(160); CASE(176); CASE(192); CASE(208); CASE(224); CASE(240); CASE(256);
@@ -588,6 +595,14 @@ static __device__ __align__(256) float g_noalloc_workspace[LLMX_NOALLOC_WS_FLOAT
 static __device__ __align__(256) unsigned int g_noalloc_counters[LLMX_NOALLOC_COUNTERS];
 
 // In host code an array's name is only a handle for the runtime, not an address a kernel can use:
+LLMX_API int llmx_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                   long long n_pages, const int* block_table, int table_width, const int* seq_past, float* ws,
+                                   unsigned int* counters, int B, int H, int G, int D, int window, float scale,
+                                   int n_chunks, cudaStream_t stream) {
+  return llmx_attention_decode_keep(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, B,
+                                    H, G, D, window, 0, scale, n_chunks, stream);
+}
+
 // the device addresses are asked for once per device, with that device current, and kept.
 #define LLMX_NOALLOC_MAX_DEVICES 64
 static float* g_noalloc_ptr[LLMX_NOALLOC_MAX_DEVICES];

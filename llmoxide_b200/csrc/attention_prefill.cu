@@ -1,5 +1,6 @@
 // Prompt attention over the paged bfloat16 cache: variable-length batches,
-// causal, grouped-query, a window or none, whole prompts or later chunks of a
+// causal, grouped-query, a window or none (under a window the first keep_first
+// keys of a sequence may stay visible), whole prompts or later chunks of a
 // prompt (queries at positions past..past+T-1 read the cached keys before
 // them too).  Tiled online-softmax attention: a CTA owns 64 consecutive query
 // tokens of one head and walks the visible keys one cache page (64 keys) at a
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
                          const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_past, int H, int G,
-                         int window, float scale_log2) {
+                         int window, int keep_first, float scale_log2) {
   constexpr int CHUNKS = D / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;             // k-steps of the score product
   constexpr int TILE_BYTES = PF_BK * D * 2;
@@ -82,8 +83,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   const int pos_lo = past + i0, pos_hi = past + i0 + rows_here - 1;   // positions of the tile's queries
   const int first_lo = (window > 0 && pos_lo - (window - 1) > 0) ? pos_lo - (window - 1) : 0;
   const int page_first = first_lo / PF_BK, page_last = pos_hi / PF_BK;
-  const int n_tiles = page_last - page_first + 1;
+  // pages that hold kept first keys and lie wholly before the window's first page are walked first
+  const int n_kept_tiles = keep_first > 0 ? min(page_first, (keep_first + PF_BK - 1) / PF_BK) : 0;
+  const int n_tiles = n_kept_tiles + page_last - page_first + 1;
   const int* pages = block_table + (size_t)b * table_width;
+  auto page_of = [&](int t) { return t < n_kept_tiles ? t : page_first + (t - n_kept_tiles); };
 
   // ---- stage the query tile -------------------------------------------------------
   for (int idx = tid; idx < PF_BQ * CHUNKS; idx += PF_THREADS) {
@@ -92,7 +96,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
     cp_async16(sQ + swz<D>(r, c), q + ((size_t)(tok0 + i0 + rr) * H + hq) * D + c * 8);
   }
   auto load_tile = [&](int t, int stage) {
-    const int phys = pages[page_first + t];
+    const int phys = pages[page_of(t)];
     const bf16* kp = k_cache + cache_row_offset(phys, g, 0, G, D);
     const bf16* vp = v_cache + cache_row_offset(phys, g, 0, G, D);
     const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
@@ -135,7 +139,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
                     qf[ks][3]);
     }
     const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
-    const int key0 = (page_first + t) * PF_BK;
+    const int key0 = page_of(t) * PF_BK;
     if (key0 + PF_BK - 1 > pos_hi) {
       // Rows of the page past the sequence's last key were never written (or belong to an earlier owner
       // of the page).  Their weights are exactly 0, but 0 * NaN is NaN, so the values are cleared.
@@ -174,8 +178,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int key = key0 + 8 * j + 2 * (lane & 3) + e;
-        s[j][e] = (key >= f0 && key <= p0) ? s[j][e] * scale_log2 : -INFINITY;
-        s[j][2 + e] = (key >= f1 && key <= p1) ? s[j][2 + e] * scale_log2 : -INFINITY;
+        s[j][e] = ((key >= f0 || key < keep_first) && key <= p0) ? s[j][e] * scale_log2 : -INFINITY;
+        s[j][2 + e] = ((key >= f1 || key < keep_first) && key <= p1) ? s[j][2 + e] * scale_log2 : -INFINITY;
         mx0 = fmaxf(mx0, s[j][e]);
         mx1 = fmaxf(mx1, s[j][2 + e]);
       }
@@ -248,7 +252,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
 template <int D>
 static int launch_prefill(const void* q, void* out, const void* k_cache, const void* v_cache, const int* block_table,
                           int table_width, const int* seq_start, const int* seq_past, int B, int max_new, int H,
-                          int G, int window, float scale, cudaStream_t stream) {
+                          int G, int window, int keep_first, float scale, cudaStream_t stream) {
   const size_t smem = (size_t)PF_BQ * D * 2 + 4 * (size_t)PF_BK * D * 2;
   auto kernel = attention_prefill_kernel<D>;
   static bool attr_set = false;
@@ -260,7 +264,7 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
   dim3 grid(H, (max_new + PF_BQ - 1) / PF_BQ, B);
   launch_pdl(kernel, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                              block_table, table_width, seq_start, seq_past, H, G, window,
-                                             scale * 1.4426950408889634f);
+                                             keep_first, scale * 1.4426950408889634f);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -270,16 +274,16 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
 LLMX_API int llmx_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,
                                     const int* block_table, int table_width, const int* seq_start,
                                     const int* seq_past, int B, int max_new, int H, int G, int D, int window,
-                                    float scale, cudaStream_t stream) {
+                                    int keep_first, float scale, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || window < 0 || B > 65535 ||
+  if (H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 ||
       (max_new + PF_BQ - 1) / PF_BQ > 65535)
     return LLMX_REFUSED(1);
   if (D == 128)
     return launch_prefill<128>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new,
-                               H, G, window, scale, stream);
+                               H, G, window, window > 0 ? keep_first : 0, scale, stream);
   if (D == 64)
     return launch_prefill<64>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new, H,
-                              G, window, scale, stream);
+                              G, window, window > 0 ? keep_first : 0, scale, stream);
   return LLMX_REFUSED(1);
 }

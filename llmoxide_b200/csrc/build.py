@@ -43,6 +43,7 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "linear_attention": (["linear_attention.cu"], []),
     "moe": (["moe.cu"], []),
+    "moe_tc": (["moe_tc.cu"], []),
     "sampling": (["sampling.cu"], []),
     "random_init": (["random_init.cu"], []),
     # host code only (no CUDA): the cache's bookkeeping and the step plan

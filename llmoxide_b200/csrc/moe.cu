@@ -128,12 +128,12 @@ LLMX_API int llmx_moe_route(const float* logits, int* ids, float* wts, int n_tok
 
 // ---------------------------------------------------------------------------
 // Sort.  One CTA.  P = n_tokens * top pairs, pair r = t * top + choice.  Out: perm[P] (sorted place -> pair),
-// tiles: for every row tile of MOE_TILE sorted rows that lie in one expert's segment, (expert, first row,
-// number of rows); unused tiles have expert -1.  max_tiles >= P / MOE_TILE + E.
+// tiles: for every row tile of tile_rows sorted rows that lie in one expert's segment, (expert, first row,
+// number of rows); the used tiles come first, unused ones have expert -1.  max_tiles >= P / tile_rows + E.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ perm, int* __restrict__ tiles,
-                int max_tiles) {
+                int max_tiles, int tile_rows) {
   __shared__ int count[MOE_MAX_EXPERTS];
   __shared__ int start[MOE_MAX_EXPERTS + 1];
   __shared__ int tile0[MOE_MAX_EXPERTS + 1];
@@ -150,7 +150,7 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ per
       start[e] = at;
       tile0[e] = tl;
       at += count[e];
-      tl += (count[e] + MOE_TILE - 1) / MOE_TILE;
+      tl += (count[e] + tile_rows - 1) / tile_rows;
     }
     start[E] = at;
     tile0[E] = tl;
@@ -158,10 +158,10 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ per
   __syncthreads();
   for (int e = tid; e < E; e += blockDim.x) {
     const int n = count[e];
-    for (int k = 0, tl = tile0[e]; k < n; k += MOE_TILE, ++tl) {
+    for (int k = 0, tl = tile0[e]; k < n; k += tile_rows, ++tl) {
       tiles[3 * tl] = e;
       tiles[3 * tl + 1] = start[e] + k;
-      tiles[3 * tl + 2] = (n - k) < MOE_TILE ? (n - k) : MOE_TILE;
+      tiles[3 * tl + 2] = (n - k) < tile_rows ? (n - k) : tile_rows;
     }
     count[e] = 0;          // reused as the segment's fill counter
   }
@@ -173,10 +173,13 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ per
   }
 }
 
-LLMX_API int llmx_moe_sort(const int* ids, int P, int E, int* perm, int* tiles, int max_tiles, cudaStream_t stream) {
+LLMX_API int llmx_moe_sort(const int* ids, int P, int E, int* perm, int* tiles, int max_tiles, int tile_rows,
+                           cudaStream_t stream) {
   if (P <= 0) return 0;
-  if (E <= 0 || E > MOE_MAX_EXPERTS || max_tiles < (P + MOE_TILE - 1) / MOE_TILE + E) return LLMX_REFUSED(1);
-  launch_pdl(moe_sort_kernel, dim3(1), dim3(P >= 4096 ? 1024 : 256), 0, stream, ids, P, E, perm, tiles, max_tiles);
+  if (E <= 0 || E > MOE_MAX_EXPERTS || tile_rows <= 0 || max_tiles < (P + tile_rows - 1) / tile_rows + E)
+    return LLMX_REFUSED(1);
+  launch_pdl(moe_sort_kernel, dim3(1), dim3(P >= 4096 ? 1024 : 256), 0, stream, ids, P, E, perm, tiles, max_tiles,
+             tile_rows);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -277,6 +280,7 @@ moe_grouped_fma_kernel(const TX* __restrict__ X, long long ldx, const TW* __rest
 
 // gated != 0: X = x [n_tokens, K] (row stride ldx), W [E, 2N, K], Y = act [P, N].
 // else:       X = act [P, K], W [E, N, K], Y = float32 [top, n_tokens, N].
+// The tile list must have been made with MOE_TILE rows per tile.
 LLMX_API int llmx_moe_grouped_fma(const void* X, int x_dtype, long long ldx, const void* W, int w_dtype, void* Y,
                                   int y_dtype, const int* perm, const int* tiles, int max_tiles,
                                   const float* pair_weight, int top, int n_tokens, int N, int K, int gated,

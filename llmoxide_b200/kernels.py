@@ -121,7 +121,7 @@ def _library(lib_name: str):
 # or a request a kernel could not serve, leaves a code there.  The host looks at the words whenever it has
 # waited for a step anyway (no copy, no extra synchronisation).
 
-_STATUS_SLOTS = {"gemm_tc": 0, "attention_prefill_tc": 1, "attention_decode": 2, "sampling": 3}
+_STATUS_SLOTS = {"gemm_tc": 0, "attention_prefill_tc": 1, "attention_decode": 2, "sampling": 3, "moe_tc": 4}
 _STATUS_MEANING = {
     "gemm_tc": {1: "the producer's wait for a free stage ran out", 2: "the MMA issuer's wait for a stage's data ran out",
                 3: "the epilogue's wait for an accumulator ran out", 4: "the MMA issuer's wait for a drained accumulator ran out",
@@ -129,6 +129,8 @@ _STATUS_MEANING = {
                 13: "CTA pair: the epilogue's wait for an accumulator ran out",
                 14: "CTA pair: the MMA issuer's wait for a drained accumulator ran out"},
     "attention_prefill_tc": {20: "its shared memory is not 1024-byte aligned"},
+    "moe_tc": {1: "the producer's wait for a free stage ran out", 2: "the MMA issuer's wait for a stage's data ran out",
+               3: "the epilogue's wait for an accumulator ran out", 4: "the MMA issuer's wait for a drained accumulator ran out"},
     "attention_decode": {1: "a copy into shared memory never completed", 2: "its shared memory is not 1024-byte aligned"},
     "sampling": {1: "top_p < 1 over more candidates than the kernel sorts", 2: "top_k beyond what the kernel sorts"},
 }
@@ -404,7 +406,7 @@ def _counters(device, n: int):
 
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
-                     head_dim: int, window, scale: float, n_chunks: int = 0) -> None:
+                     head_dim: int, window, scale: float, n_chunks: int = 0, keep_first: int = 0) -> None:
     """One new token per sequence, bfloat16: q, out [B,H*D] in batch order;
     seq_past[b] is the token's position.  Each sequence's keys are split over
     n_chunks CTAs (0: chosen from the batch's shape), which merge inside a
@@ -417,7 +419,7 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
     B = q.shape[0]
     n_pages = block_table.shape[1]
     if window:
-        n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1)
+        n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1 + (int(keep_first or 0) + PAGE - 1) // PAGE)
     group = n_heads // n_kv_heads
     n_chunks = n_chunks or decode_chunks(B, n_kv_heads, group, n_pages, n_sm(q.device))
     ws = counters = None
@@ -425,13 +427,13 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
         ws = guard.scratch((B * n_heads * n_chunks * (head_dim + 4),), torch.float32, q.device,
                            "decode attention workspace")
         counters = _counters(q.device, B * n_kv_heads * ((group + 7) // 8))
-    f = _fn("attention_decode", "llmx_attention_decode",
+    f = _fn("attention_decode", "llmx_attention_decode_keep",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1],
-             _ptr(seq_past), _ptr(ws), _ptr(counters), B, n_heads, n_kv_heads, head_dim, int(window or 0), scale,
-             n_chunks, _stream()), "attention_decode")
+             _ptr(seq_past), _ptr(ws), _ptr(counters), B, n_heads, n_kv_heads, head_dim, int(window or 0),
+             int(keep_first or 0), scale, n_chunks, _stream()), "attention_decode")
 
 
 def attention_decode_status() -> int:
@@ -446,19 +448,19 @@ def attention_prefill_supports(q, k_cache, head_dim: int) -> bool:
 
 
 def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
-                      n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float) -> None:
+                      n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0) -> None:
     """Prompt attention on the tensor cores, bfloat16, head sizes 64 and 128:
-    q, out [T,H*D] packed sequence after sequence."""
+    q, out [T,H*D] packed sequence after sequence.  Under a window the first ``keep_first`` keys stay visible."""
     _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
     if not attention_prefill_supports(q, k_cache, head_dim):
         raise Unsupported(f"the tiled prompt attention takes bfloat16 and head sizes 64 or 128, not {head_dim}")
     f = _fn("attention_prefill", "llmx_attention_prefill",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(seq_start), _ptr(seq_past), n_seqs, max_new, n_heads, n_kv_heads, head_dim, int(window or 0),
-             scale, _stream()), "attention_prefill")
+             int(keep_first or 0), scale, _stream()), "attention_prefill")
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
@@ -684,17 +686,50 @@ def moe_route(logits, ids, weights, top: int, n_groups: int, keep_groups: int, g
              int(normalize), norm_eps, scale, _stream()), "moe_route")
 
 
-def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
-    return (n_pairs + MOE_TILE - 1) // MOE_TILE + n_experts
+def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int = MOE_TILE) -> int:
+    return (n_pairs + tile_rows - 1) // tile_rows + n_experts
 
 
-def moe_sort(ids, n_experts: int, perm, tiles) -> None:
+def moe_sort(ids, n_experts: int, perm, tiles, tile_rows: int = MOE_TILE) -> None:
     """Orders the (token, choice) pairs by expert: ``perm`` int32 [P] (sorted place -> pair) and ``tiles``
-    int32 [max_tiles, 3] (expert or -1, first row, rows)."""
+    int32 [max_tiles, 3] (expert or -1, first row, rows), of up to ``tile_rows`` rows each."""
     _dev(ids, perm, tiles)
     _contig("ids", ids), _contig("perm", perm), _contig("tiles", tiles)
-    f = _fn("moe", "llmx_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
-    _check(f(_ptr(ids), ids.numel(), n_experts, _ptr(perm), _ptr(tiles), tiles.shape[0], _stream()), "moe_sort")
+    f = _fn("moe", "llmx_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(ids), ids.numel(), n_experts, _ptr(perm), _ptr(tiles), tiles.shape[0], tile_rows, _stream()),
+           "moe_sort")
+
+
+def moe_tc_supports(x, w) -> bool:
+    """Shapes the tensor-core grouped product takes: bfloat16, K a multiple of 8, 16-byte aligned rows."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def moe_gather_rows(x, perm, top: int, xs) -> None:
+    """xs[place] = x[perm[place] // top]: the tokens' rows in the sorted order of their pairs (bfloat16)."""
+    _dev(x, perm, xs)
+    _contig("xs", xs)
+    assert x.dtype == torch.bfloat16 and xs.dtype == torch.bfloat16 and xs.shape == (perm.numel(), x.shape[1])
+    f = _fn("moe_tc", "llmx_moe_gather_rows", [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(perm), top, _ptr(xs), perm.numel(), x.shape[1], _stream()), "moe_gather_rows")
+
+
+def moe_grouped_tc(xs, w, y, perm, tiles, tile_rows: int, pair_weight, top: int, n_tokens: int, gated: bool) -> None:
+    """The grouped products on tcgen05.  ``xs`` bfloat16 [P, K] in sorted order; ``gated``: w [E, 2F, K] (gate rows,
+    then up rows), y bfloat16 [P, F]; else w [E, N, K], y float32 [top, T, N] = weight of the pair times the product.
+    ``tiles`` made by ``moe_sort`` with ``tile_rows`` in (16, 64, 128)."""
+    _dev(xs, w, y, perm, tiles, pair_weight)
+    _contig("w", w), _contig("y", y)
+    assert moe_tc_supports(xs, w) and tile_rows in (16, 64, 128)
+    K = xs.shape[1]
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    assert w.shape[2] == K and y.dtype == (torch.bfloat16 if gated else torch.float32)
+    f = _fn("moe_tc", "llmx_moe_grouped_tc",
+            [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(xs), xs.stride(0), xs.shape[0], _ptr(w), w.shape[0], _ptr(y), _ptr(tiles), tiles.shape[0], tile_rows,
+             _ptr(perm), _ptr(pair_weight), top, n_tokens, N, K, int(gated), _stream()), "moe_grouped_tc")
 
 
 def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gated: bool) -> None:

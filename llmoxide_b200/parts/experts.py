@@ -66,8 +66,18 @@ class RoutedExperts:
         del gate_up
         self.down = torch.stack([weights.pop(t[f"down{e}"].name).to(dt) for e in range(self.E)]).contiguous()  # [E, d, F]
 
+        # bfloat16 with sizes the TMA takes: the grouped products run on tcgen05 (csrc/moe_tc.cu)
+        self.tensor_cores = bool(rt.tensor_cores and dt == torch.bfloat16 and self.gate_up.shape[2] % 8 == 0
+                                 and self.F % 8 == 0)
+
     def libraries(self) -> set:
-        return {"moe"} | self.router.libraries()
+        return {"moe"} | ({"moe_tc"} if self.tensor_cores else set()) | self.router.libraries()
+
+    def tile_rows(self, n_pairs: int) -> int:
+        """Rows per tile of the grouped products: narrow tiles when an expert gets few rows (a decode step streams
+        the weights), wide ones for prompts."""
+        per_expert = n_pairs / self.E
+        return 16 if per_expert <= 16 else 64 if per_expert <= 96 else 128
 
     def forward(self, x, ctx, residual=None):
         T, dev = x.shape[0], x.device
@@ -78,10 +88,18 @@ class RoutedExperts:
         kernels.moe_route(logits, ids, pair_w, self.top, self.n_groups, self.keep_groups, self.group_top, self.score,
                           self.normalize, self.norm_eps, self.scale)
         perm = torch.empty((P,), dtype=torch.int32, device=dev)
-        tiles = torch.empty((kernels.moe_max_tiles(P, self.E), 3), dtype=torch.int32, device=dev)
-        kernels.moe_sort(ids, self.E, perm, tiles)
+        fast = self.tensor_cores and x.dtype == torch.bfloat16 and kernels.moe_tc_supports(x, self.gate_up)
+        rows = self.tile_rows(P) if fast else kernels.MOE_TILE
+        tiles = torch.empty((kernels.moe_max_tiles(P, self.E, rows), 3), dtype=torch.int32, device=dev)
+        kernels.moe_sort(ids, self.E, perm, tiles, rows)
         act = torch.empty((P, self.F), dtype=self.rt.act_dtype, device=dev)
-        kernels.moe_grouped(x, self.gate_up, act, perm, tiles, pair_w, self.top, T, gated=True)
         y = torch.empty((self.top, T, self.down.shape[1]), dtype=torch.float32, device=dev)
-        kernels.moe_grouped(act, self.down, y, perm, tiles, pair_w, self.top, T, gated=False)
+        if fast:
+            xs = torch.empty((P, x.shape[1]), dtype=torch.bfloat16, device=dev)
+            kernels.moe_gather_rows(x, perm, self.top, xs)
+            kernels.moe_grouped_tc(xs, self.gate_up, act, perm, tiles, rows, pair_w, self.top, T, gated=True)
+            kernels.moe_grouped_tc(act, self.down, y, perm, tiles, rows, pair_w, self.top, T, gated=False)
+        else:
+            kernels.moe_grouped(x, self.gate_up, act, perm, tiles, pair_w, self.top, T, gated=True)
+            kernels.moe_grouped(act, self.down, y, perm, tiles, pair_w, self.top, T, gated=False)
         return y
