@@ -466,7 +466,7 @@ def design_bench(args) -> int:
                 elif name == "llmx_gemm_fma":
                     tag += f" N{a[7]} K{a[8]}"
                 elif name == "llmx_moe_grouped_tc":
-                    tag += " gate|up" if a[15] else " down"
+                    tag += " gate|up" if a[13] else " down"
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 code = f(*a)

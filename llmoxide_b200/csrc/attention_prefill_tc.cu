@@ -1,6 +1,7 @@
 // Prompt attention on the 5th-generation tensor cores (tcgen05), head size 128,
 // bfloat16, over the paged cache: variable-length batches, causal,
-// grouped-query, a window or none, whole prompts or later chunks of one.
+// grouped-query, a window or none (under a window the sequence's first keep_first keys may stay visible), whole
+// prompts or later chunks of one.
 //
 // Formulas as in attention.cu (crates/model/src/qwen35/cpu.rs:325-355,
 // crates/model/src/cache.rs:31-37); the step's keys and values are in the cache
@@ -58,7 +59,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
-                            const int* __restrict__ seq_past, int H, int G, int window, float scale_log2) {
+                            const int* __restrict__ seq_past, int H, int G, int window, int keep_first,
+                            float scale_log2) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_launch_dependents();
   pdl_wait();
@@ -75,7 +77,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int pos_lo = past + i0, pos_hi = past + i0 + rows_here - 1;
   const int first_lo = (window > 0 && pos_lo - (window - 1) > 0) ? pos_lo - (window - 1) : 0;
   const int tile_first = first_lo / AT_KEYS, tile_last = pos_hi / AT_KEYS;
-  const int n_tiles = tile_last - tile_first + 1;
+  // Under a window that keeps the sequence's first keys, the tiles that hold those and lie wholly before the
+  // window's first tile are walked first: place j of the walk is tile j, or past them tile_first + (j - n_kept).
+  const int n_kept = keep_first > 0 ? min(tile_first, (keep_first + AT_KEYS - 1) / AT_KEYS) : 0;
+  const int n_tiles = n_kept + tile_last - tile_first + 1;
+  auto tile_at = [&](int j) { return j < n_kept ? j : tile_first + (j - n_kept); };
   const int* pages = block_table + (size_t)b * table_width;
 
   // shared memory: Q (32 KB), K[2], V[2] (16 KB each), then barriers
@@ -133,7 +139,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t parity = ((j >> 1) & 1) ^ 1;
-        const int row = (pages[tile_first + j] * G + g) * LLMX_PAGE;      // the tile is one page of one kv head
+        const int row = (pages[tile_at(j)] * G + g) * LLMX_PAGE;          // the tile is one page of one kv head
         if (!mbar_wait(s_full0 + 8u * st, parity)) { at_report(1); break; }
         mbar_expect_tx(k_full0 + 8u * st, AT_KTILE);
         tma_load_2d(sK0 + (uint32_t)st * AT_KTILE, &map_k, 0, row, k_full0 + 8u * st);
@@ -200,7 +206,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!ok) break;
       tc_fence_after();
       const uint32_t tS = tS0 + (uint32_t)st * AT_KEYS + lane_off;
-      const int key0 = (tile_first + j) * AT_KEYS;
+      const int key0 = tile_at(j) * AT_KEYS;
       // the row of S: four loads in flight, one wait
       uint32_t sr[AT_KEYS];
 #pragma unroll
@@ -214,7 +220,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int e = 0; e < AT_KEYS; ++e) {
           const int key = key0 + e;
-          if (!(row_live && key >= first && key <= pos)) sr[e] = 0xff800000u;     // -inf
+          if (!(row_live && (key >= first || key < keep_first) && key <= pos)) sr[e] = 0xff800000u;     // -inf
         }
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, so the maxima overlap
@@ -337,9 +343,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,
                                        long long n_pages, const int* block_table, int table_width,
                                        const int* seq_start, const int* seq_past, int B, int T, int max_new, int H,
-                                       int G, int D, int window, float scale, cudaStream_t stream) {
+                                       int G, int D, int window, int keep_first, float scale, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0 || T <= 0) return 0;
-  if (D != AT_D || H <= 0 || G <= 0 || H % G || window < 0 || B > 65535 || (max_new + AT_ROWS - 1) / AT_ROWS > 65535 || n_pages <= 0)
+  if (window <= 0) keep_first = 0;
+  if (D != AT_D || H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 || (max_new + AT_ROWS - 1) / AT_ROWS > 65535 || n_pages <= 0)
     return LLMX_REFUSED(1);
   if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return LLMX_REFUSED(1);
   CUtensorMap mq, mk, mv;
@@ -361,7 +368,7 @@ LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_c
   }
   dim3 grid(H, (max_new + AT_ROWS - 1) / AT_ROWS, B);
   launch_pdl(attention_prefill_tc_kernel, grid, dim3(AT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, block_table,
-             table_width, seq_start, seq_past, H, G, window, scale * 1.4426950408889634f);
+             table_width, seq_start, seq_past, H, G, window, keep_first, scale * 1.4426950408889634f);
   return LLMX_LAUNCH_STATUS();
 }
 

@@ -5,9 +5,9 @@
 //   o_t = S_t^T q_t
 //
 // q, k and v come out of one fused projection (a row holds q heads, k heads, v heads and the gate's columns).
-// What the design does to them before the recurrence happens while a chunk of tokens is staged in shared
-// memory: an activation (none or SiLU), the rotation of q and k (pairs (i, i + n_rot/2) of a head's first
-// n_rot dims, angle from float32 tables), a scale on k.  All of it, the state and the sums are float32.
+// What the design does to them before the recurrence is done by a kernel of its own, once per (token, head):
+// an activation (none or SiLU), the rotation of q and k (pairs (i, i + n_rot/2) of a head's first n_rot dims,
+// angle from float32 tables), a scale on k.  All of it, the state and the sums are float32.
 //
 // The recurrence is independent for every column of v, so a CTA owns `cols` columns of one (sequence, head)
 // and walks that sequence's tokens of the step in order.  Within a CTA a warp owns 4 columns; the 8 lanes of
@@ -21,7 +21,9 @@
 // step, which is what bounds a decode step.
 #include "common.cuh"
 
-#define LA_CHUNK 16          // tokens staged per round
+#define LA_CHUNK 8           // tokens per staged chunk
+#define LA_STAGES 3          // chunks in flight or in use
+#define LA_SEG 128           // tokens per segment of a long prompt
 #define LA_MAX_D 256
 
 enum { LA_ACT_NONE = 0, LA_ACT_SILU = 1, LA_ACT_SIGMOID = 2 };
@@ -40,148 +42,275 @@ __device__ __forceinline__ float la_value(const TIN* row, int c, int n_split, si
   return v;
 }
 
-// DPT: dims of D per thread (a multiple of 4; 8 threads share a column, so D <= 8 DPT).
-template <typename TIN, int DPT>
-__global__ void __launch_bounds__(256)
-decay_scan_kernel(const TIN* __restrict__ proj, int n_split, size_t split_stride, size_t row_stride,
-                  int q_off, int k_off, int v_off, float* __restrict__ out, float* __restrict__ state,
-                  const int* __restrict__ seq_start, const int* __restrict__ seq_past,
-                  const int* __restrict__ seq_slot, const float* __restrict__ decay,
-                  const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_rot, int act,
-                  float k_scale, int H, int D, int Dv, int cols) {
-  extern __shared__ float la_smem[];
-  const int Dp = (D + 3) & ~3;                    // staged rows are padded to a multiple of 4 dims
-  float* qs = la_smem;                            // [LA_CHUNK][Dp]
-  float* ks = qs + LA_CHUNK * Dp;                 // [LA_CHUNK][Dp]
-  float* vs = ks + LA_CHUNK * Dp;                 // [LA_CHUNK][cols]
+// Before the recurrence: what the design does to q, k and v, once per (token, head), into float32 rows
+// prep[t][h] = (q[Dp], k[Dp], v[Dvp]) with Dp, Dvp the sizes rounded up to 4 (the padding is zero).
+template <typename TIN>
+__global__ void __launch_bounds__(128)
+decay_prep_kernel(const TIN* __restrict__ proj, int n_split, size_t split_stride, size_t row_stride, int q_off,
+                  int k_off, int v_off, float* __restrict__ prep, const int* __restrict__ token_pos,
+                  const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_rot, int act, float k_scale,
+                  int H, int D, int Dv) {
   pdl_launch_dependents();
-  const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * cols;
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int Dp = (D + 3) & ~3, Dvp = (Dv + 3) & ~3;
+  const int pos = token_pos[t], half = n_rot >> 1;
+  pdl_wait();
+  const TIN* row = proj + (size_t)t * row_stride;
+  const TIN* qrow = row + q_off + h * D;
+  const TIN* krow = row + k_off + h * D;
+  const TIN* vrow = row + v_off + h * Dv;
+  float* out = prep + ((size_t)t * H + h) * (size_t)(2 * Dp + Dvp);
+  for (int d = threadIdx.x; d < Dp; d += blockDim.x) {
+    float qv = 0.f, kv = 0.f;
+    if (d < D) {
+      qv = la_act(la_value(qrow, d, n_split, split_stride), act);
+      kv = la_act(la_value(krow, d, n_split, split_stride), act);
+      if (d < n_rot) {
+        const int i = d < half ? d : d - half;
+        const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+        const int partner = d < half ? d + half : d - half;
+        const float qp = la_act(la_value(qrow, partner, n_split, split_stride), act);
+        const float kp = la_act(la_value(krow, partner, n_split, split_stride), act);
+        // (u, v) -> (u cos - v sin, v cos + u sin) for the pair (i, i + half)
+        qv = d < half ? qv * c - qp * s : qv * c + qp * s;
+        kv = d < half ? kv * c - kp * s : kv * c + kp * s;
+      }
+      kv *= k_scale;
+    }
+    out[d] = qv;
+    out[Dp + d] = kv;
+  }
+  for (int c = threadIdx.x; c < Dvp; c += blockDim.x)
+    out[2 * Dp + c] = c < Dv ? la_act(la_value(vrow, c, n_split, split_stride), act) : 0.f;
+}
+
+__device__ __forceinline__ void la_cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void la_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void la_cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// The recurrence over the prepared rows.  Chunks of LA_CHUNK tokens come into a ring of LA_STAGES buffers by
+// 16-byte asynchronous copies, two chunks ahead of the one being walked.
+//
+// A long prompt is cut into segments of seg_len tokens that run side by side (a sequence alone would keep only
+// H * Dv / cols CTAs busy).  PASS 1: every segment runs the recurrence, the first from the stored state, the
+// others from zero, and leaves its last state in `partial` (a sequence of one segment writes the state itself).
+// PASS 2, for the segments after the first: the state the segment should have started from, E, is put together
+// from the segments before it (E_0 = partial_0, E_s = decay^seg_len E_(s-1) + partial_s); a token i of the
+// segment then lacks decay^(i+1) E^T q_i, which is added to its output; the last segment also writes the
+// sequence's new state.  Segments are counted from the step's first token of a sequence, so a sum may be
+// rounded differently when a prompt is cut differently; a step of up to seg_len tokens per sequence (every
+// decode step) is the plain recurrence.
+// DPT: dims of D per thread (a multiple of 4; 8 threads share a column, so D <= 8 DPT).
+template <int DPT, int PASS>
+__global__ void __launch_bounds__(256)
+decay_scan_kernel(const float* __restrict__ prep, float* __restrict__ out, float* __restrict__ state,
+                  float* __restrict__ partial, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                  const float* __restrict__ decay, int H, int D, int Dv, int cols, int col_blocks, int seg_len,
+                  int n_seg_max) {
+  extern __shared__ __align__(16) float la_smem[];
+  const int Dp = (D + 3) & ~3, Dvp = (Dv + 3) & ~3;
+  const int row_len = 2 * Dp + Dvp;               // floats per (token, head) of prep
+  const int tok_len = 2 * Dp + cols;              // floats per staged token: q, k, this CTA's columns of v
+  pdl_launch_dependents();
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int seg = blockIdx.x / col_blocks, c0 = (blockIdx.x - seg * col_blocks) * cols;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int col = c0 + warp * 4 + (lane >> 3);    // this thread's column of v
   const int r = lane & 7;                         // its share of D
-  const bool col_live = (warp * 4 + (lane >> 3)) < cols && col < Dv;
-  const int t0 = seq_start[b], n_new = seq_start[b + 1] - t0, past = seq_past[b];
+  const bool col_live = col < Dv;
+  const int seq_t0 = seq_start[b], seq_new = seq_start[b + 1] - seq_t0;
+  const int n_seg = (seq_new + seg_len - 1) / seg_len;        // this sequence's segments
   const float g = decay[h];
   float* S = state + ((size_t)seq_slot[b] * H + h) * (size_t)D * Dv;
-  const int half = n_rot >> 1;
+  if (seg >= n_seg || (PASS == 2 && (n_seg == 1 || seg == 0))) return;       // (uniform over the CTA)
+  const int t0 = seq_t0 + seg * seg_len;                                      // the segment's first token
+  const int n_new = min(seg_len, seq_new - seg * seg_len);
+  float* part_seq = partial ? partial + ((size_t)b * H + h) * (size_t)n_seg_max * D * Dv : nullptr;
   pdl_wait();
 
+  auto own = [&](int i) { return 4 * (r + 8 * (i >> 2)) + (i & 3); };        // dim of this thread's i-th state value
   float s_reg[DPT];
+  if (PASS == 1) {
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) {
-    const int d = 4 * (r + 8 * (i >> 2)) + (i & 3);
-    s_reg[i] = (col_live && d < D) ? S[(size_t)d * Dv + col] : 0.f;
+    for (int i = 0; i < DPT; ++i) s_reg[i] = (seg == 0 && col_live && own(i) < D) ? S[(size_t)own(i) * Dv + col] : 0.f;
+  } else {
+    // E_(seg-1): what the segments before left, each decayed over the segments after it
+    float g_seg = 1.f;
+    for (int i = 0; i < seg_len; ++i) g_seg *= g;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) s_reg[i] = 0.f;
+    for (int sp = 0; sp < seg; ++sp) {
+      const float* ps = part_seq + (size_t)sp * D * Dv;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i)
+        if (col_live && own(i) < D) s_reg[i] = fmaf(g_seg, s_reg[i], __ldcg(ps + (size_t)own(i) * Dv + col));
+    }
   }
 
-  for (int base = 0; base < n_new; base += LA_CHUNK) {
+  const int n_chunks = (n_new + LA_CHUNK - 1) / LA_CHUNK;
+  const int qk_pieces = (PASS == 1 ? 2 : 1) * Dp / 4, v_pieces = PASS == 1 ? cols / 4 : 0, pieces = qk_pieces + v_pieces;
+  auto load_chunk = [&](int chunk) {
+    float* buf = la_smem + (size_t)(chunk % LA_STAGES) * LA_CHUNK * tok_len;
+    const int base = chunk * LA_CHUNK;
     const int n_tok = (n_new - base) < LA_CHUNK ? (n_new - base) : LA_CHUNK;
-    __syncthreads();                              // the chunk before has been consumed
-    // stage q and k of the chunk: activation, rotation, scale
-    for (int e = tid; e < n_tok * Dp; e += blockDim.x) {
-      const int tt = e / Dp, d = e - tt * Dp;
-      float qv = 0.f, kv = 0.f;
-      if (d < D) {
-        const TIN* row = proj + (size_t)(t0 + base + tt) * row_stride;
-        const TIN* qrow = row + q_off + h * D;
-        const TIN* krow = row + k_off + h * D;
-        qv = la_act(la_value(qrow, d, n_split, split_stride), act);
-        kv = la_act(la_value(krow, d, n_split, split_stride), act);
-        if (d < n_rot) {
-          const int pos = past + base + tt;
-          const int i = d < half ? d : d - half;
-          const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
-          const int partner = d < half ? d + half : d - half;
-          const float qp = la_act(la_value(qrow, partner, n_split, split_stride), act);
-          const float kp = la_act(la_value(krow, partner, n_split, split_stride), act);
-          // (u, v) -> (u cos - v sin, v cos + u sin) for the pair (i, i + half)
-          qv = d < half ? qv * c - qp * s : qv * c + qp * s;
-          kv = d < half ? kv * c - kp * s : kv * c + kp * s;
-        }
-        kv *= k_scale;
-      }
-      qs[e] = qv;
-      ks[e] = kv;
-    }
-    for (int e = tid; e < n_tok * cols; e += blockDim.x) {
-      const int tt = e / cols, c = e - tt * cols;
-      float v = 0.f;
-      if (c0 + c < Dv) {
-        const TIN* vrow = proj + (size_t)(t0 + base + tt) * row_stride + v_off + h * Dv;
-        v = la_act(la_value(vrow, c0 + c, n_split, split_stride), act);
-      }
-      vs[e] = v;
-    }
-    __syncthreads();
     for (int tt = 0; tt < n_tok; ++tt) {
-      const float v = vs[tt * cols + warp * 4 + (lane >> 3)];
-      const float* qrow = qs + tt * Dp;
-      const float* krow = ks + tt * Dp;
-      float acc = 0.f;
+      const float* src = prep + ((size_t)(t0 + base + tt) * H + h) * row_len;
+      float* dst = buf + tt * tok_len;
+      for (int pc = tid; pc < pieces; pc += blockDim.x) {
+        if (pc < qk_pieces) la_cp_async16(dst + 4 * pc, src + 4 * pc);
+        else if (c0 + 4 * (pc - qk_pieces) < Dvp) la_cp_async16(dst + 2 * Dp + 4 * (pc - qk_pieces), src + 2 * Dp + c0 + 4 * (pc - qk_pieces));
+      }
+    }
+  };
+  for (int c = 0; c < LA_STAGES - 1; ++c) {
+    if (c < n_chunks) load_chunk(c);
+    la_cp_async_commit();
+  }
+  float g_pow = g;                                 // PASS 2: decay^(i+1) for the token at hand
+  for (int chunk = 0; chunk < n_chunks; ++chunk) {
+    if (chunk + LA_STAGES - 1 < n_chunks) load_chunk(chunk + LA_STAGES - 1);     // into the buffer walked last round
+    la_cp_async_commit();
+    la_cp_async_wait<LA_STAGES - 1>();            // this chunk's copies have landed
+    __syncthreads();
+    const float* buf = la_smem + (size_t)(chunk % LA_STAGES) * LA_CHUNK * tok_len;
+    const int base = chunk * LA_CHUNK;
+    const int n_tok = (n_new - base) < LA_CHUNK ? (n_new - base) : LA_CHUNK;
+    // one token.  PASS 1: S = g S + k v, then this thread's share of q . S.  PASS 2: its share of q . E.  The
+    // shares are added and stored afterwards, so that in a full chunk (the loop below unrolls) one token's
+    // shuffles overlap the next token's arithmetic.
+    auto one_token = [&](int tt) {
+      const float* qrow = buf + tt * tok_len;
+      const float* krow = qrow + Dp;
+      const float v = (PASS == 1 && col_live) ? qrow[2 * Dp + warp * 4 + (lane >> 3)] : 0.f;
+      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
       for (int i4 = 0; i4 < DPT / 4; ++i4) {
         const int d = 4 * (r + 8 * i4);
         if (d < Dp) {
-          const float4 k4 = *reinterpret_cast<const float4*>(krow + d);
           const float4 q4 = *reinterpret_cast<const float4*>(qrow + d);
           float* s4 = s_reg + 4 * i4;
-          s4[0] = fmaf(g, s4[0], k4.x * v);
-          s4[1] = fmaf(g, s4[1], k4.y * v);
-          s4[2] = fmaf(g, s4[2], k4.z * v);
-          s4[3] = fmaf(g, s4[3], k4.w * v);
-          acc = fmaf(s4[0], q4.x, acc);
-          acc = fmaf(s4[1], q4.y, acc);
-          acc = fmaf(s4[2], q4.z, acc);
-          acc = fmaf(s4[3], q4.w, acc);
+          if (PASS == 1) {
+            const float4 k4 = *reinterpret_cast<const float4*>(krow + d);
+            s4[0] = fmaf(g, s4[0], k4.x * v);
+            s4[1] = fmaf(g, s4[1], k4.y * v);
+            s4[2] = fmaf(g, s4[2], k4.z * v);
+            s4[3] = fmaf(g, s4[3], k4.w * v);
+          }
+          acc0 = fmaf(s4[0], q4.x, acc0);
+          acc1 = fmaf(s4[1], q4.y, acc1);
+          acc2 = fmaf(s4[2], q4.z, acc2);
+          acc3 = fmaf(s4[3], q4.w, acc3);
         }
       }
+      return (acc0 + acc1) + (acc2 + acc3);
+    };
+    auto finish = [&](int tt, float acc) {
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (r == 0 && col_live) out[(size_t)(t0 + base + tt) * H * Dv + (size_t)h * Dv + col] = acc;
-    }
-  }
+      float* dst = out + (size_t)(t0 + base + tt) * H * Dv + (size_t)h * Dv + col;
+      if (PASS == 1) {
+        if (r == 0 && col_live) *dst = acc;
+      } else {
+        if (r == 0 && col_live) *dst += g_pow * acc;
+        g_pow *= g;
+      }
+    };
+    if (n_tok == LA_CHUNK) {
+      float part[LA_CHUNK];
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) {
-    const int d = 4 * (r + 8 * (i >> 2)) + (i & 3);
-    if (col_live && d < D) S[(size_t)d * Dv + col] = s_reg[i];
+      for (int tt = 0; tt < LA_CHUNK; ++tt) part[tt] = one_token(tt);
+#pragma unroll
+      for (int tt = 0; tt < LA_CHUNK; ++tt) finish(tt, part[tt]);
+    } else {
+      for (int tt = 0; tt < n_tok; ++tt) finish(tt, one_token(tt));
+    }
+    __syncthreads();                              // the buffer is refilled by the next round's copies
+  }
+  if (PASS == 1) {
+    float* dst = n_seg == 1 ? S : part_seq + (size_t)seg * D * Dv;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i)
+      if (col_live && own(i) < D) dst[(size_t)own(i) * Dv + col] = s_reg[i];
+  } else if (seg == n_seg - 1) {
+    // the sequence's new state: E_(n_seg-1) = decay^(its length) E_(n_seg-2) + partial_(n_seg-1)
+    float g_len = 1.f;
+    for (int i = 0; i < n_new; ++i) g_len *= g;
+    const float* ps = part_seq + (size_t)seg * D * Dv;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i)
+      if (col_live && own(i) < D)
+        S[(size_t)own(i) * Dv + col] = fmaf(g_len, s_reg[i], __ldcg(ps + (size_t)own(i) * Dv + col));
   }
 }
 
-// proj: [T, row_stride] (or split partials of it); out: float32 [T, H*Dv]; state: float32 [slots, H, D, Dv].
+// proj: [T, row_stride] (or split partials of it); prep: float32 scratch of T * H * (2 Dp + Dvp) elements, 16-byte
+// aligned; out: float32 [T, H*Dv]; state: float32 [slots, H, D, Dv].  max_new: most tokens of one sequence;
+// seg_len: tokens per segment (0: LA_SEG); partial: float32 scratch [n_seqs, H, ceil(max_new / seg_len), D, Dv],
+// needed when max_new > seg_len.
 LLMX_API int llmx_decay_scan(const void* proj, int in_dtype, int n_split, long long split_stride, long long row_stride,
-                             int q_off, int k_off, int v_off, float* out, float* state, const int* seq_start,
-                             const int* seq_past, const int* seq_slot, const float* decay, const float* cos_t,
-                             const float* sin_t, int n_rot, int act, float k_scale, int n_seqs, int H, int D, int Dv,
-                             int n_sm, cudaStream_t stream) {
-  if (n_seqs <= 0) return 0;
+                             int q_off, int k_off, int v_off, float* prep, float* out, float* state, float* partial,
+                             const int* seq_start, const int* token_pos, const int* seq_slot, const float* decay,
+                             const float* cos_t, const float* sin_t, int n_rot, int act, float k_scale, int n_tokens,
+                             int n_seqs, int max_new, int seg_len, int H, int D, int Dv, int n_sm, cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return 0;
   if (H <= 0 || D <= 0 || D > LA_MAX_D || Dv <= 0 || n_split < 1 || n_rot < 0 || n_rot > D || (n_rot & 1))
     return LLMX_REFUSED(1);
   if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
   if (act != LA_ACT_NONE && act != LA_ACT_SILU) return LLMX_REFUSED(1);
-  if (n_seqs > 65535 || H > 65535) return LLMX_REFUSED(3);
+  if (n_seqs > 65535 || H > 65535 || ((uintptr_t)prep & 15)) return LLMX_REFUSED(3);
+  if (seg_len <= 0) seg_len = LA_SEG;
+  if (max_new <= 0 || max_new > n_tokens) max_new = n_tokens;
+  const int n_seg = (max_new + seg_len - 1) / seg_len;
+  if (n_seg > 1 && !partial) return LLMX_REFUSED(4);
+  const dim3 pgrid(n_tokens, H);
+  if (in_dtype == LLMX_F32)
+    launch_pdl(decay_prep_kernel<float>, pgrid, dim3(128), 0, stream, (const float*)proj, n_split, (size_t)split_stride,
+               (size_t)row_stride, q_off, k_off, v_off, prep, token_pos, cos_t, sin_t, n_rot, act, k_scale, H, D, Dv);
+  else if (in_dtype == LLMX_BF16)
+    launch_pdl(decay_prep_kernel<bf16>, pgrid, dim3(128), 0, stream, (const bf16*)proj, n_split, (size_t)split_stride,
+               (size_t)row_stride, q_off, k_off, v_off, prep, token_pos, cos_t, sin_t, n_rot, act, k_scale, H, D, Dv);
+  else
+    return LLMX_REFUSED(2);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
   // columns per CTA: as many as still give every SM a CTA or two (a CTA with more columns stages q and k fewer times)
   int cols = 32;
-  while (cols > 8 && (long long)n_seqs * H * ((Dv + cols - 1) / cols) < 2LL * n_sm) cols >>= 1;
+  while (cols > 8 && (long long)n_seqs * H * n_seg * ((Dv + cols - 1) / cols) < 2LL * n_sm) cols >>= 1;
   while (cols > 4 && cols / 2 >= Dv) cols >>= 1;
   const int Dp = (D + 3) & ~3;
-  dim3 grid((Dv + cols - 1) / cols, H, n_seqs), block(cols * 8);
-  const size_t smem = (size_t)LA_CHUNK * (2 * Dp + cols) * sizeof(float);
-#define GO(TIN, DPT)                                                                                               \
-  launch_pdl(decay_scan_kernel<TIN, DPT>, grid, block, smem, stream, (const TIN*)proj, n_split, (size_t)split_stride, \
-             (size_t)row_stride, q_off, k_off, v_off, out, state, seq_start, seq_past, seq_slot, decay, cos_t, sin_t, \
-             n_rot, act, k_scale, H, D, Dv, cols)
-#define BY_D(TIN)                  \
-  do {                             \
-    if (Dp <= 32) GO(TIN, 4);      \
-    else if (Dp <= 64) GO(TIN, 8); \
-    else if (Dp <= 128) GO(TIN, 16); \
-    else GO(TIN, 32);              \
+  const int col_blocks = (Dv + cols - 1) / cols;
+  if ((long long)col_blocks * n_seg > 0x7fffffff) return LLMX_REFUSED(3);
+  dim3 grid(col_blocks * n_seg, H, n_seqs), block(cols * 8);
+  const size_t smem = (size_t)LA_STAGES * LA_CHUNK * (2 * Dp + cols) * sizeof(float);
+#define GO1(DPT, PASS)                                                                                                 \
+  do {                                                                                                                 \
+    static bool attr_set = false;                                                                                      \
+    if (!attr_set && smem > 48 * 1024) {                                                                               \
+      e = cudaFuncSetAttribute(decay_scan_kernel<DPT, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+      if (e != cudaSuccess) return (int)e;                                                                             \
+      attr_set = true;                                                                                                 \
+    }                                                                                                                  \
+    launch_pdl(decay_scan_kernel<DPT, PASS>, grid, block, smem, stream, (const float*)prep, out, state, partial,       \
+               seq_start, seq_slot, decay, H, D, Dv, cols, col_blocks, seg_len, n_seg);                                \
   } while (0)
-  if (in_dtype == LLMX_F32) BY_D(float);
-  else if (in_dtype == LLMX_BF16) BY_D(bf16);
-  else return LLMX_REFUSED(2);
-#undef BY_D
+#define GO(DPT)                    \
+  do {                             \
+    GO1(DPT, 1);                   \
+    if (n_seg > 1) GO1(DPT, 2);    \
+  } while (0)
+  if (Dp <= 32) GO(4);
+  else if (Dp <= 64) GO(8);
+  else if (Dp <= 128) GO(16);
+  else GO(32);
 #undef GO
+#undef GO1
   return LLMX_LAUNCH_STATUS();
 }
 

@@ -33,18 +33,12 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
-                                 int n_tokens, int E, int top, int n_groups, int keep_groups, int group_top,
-                                 int score_kind, int normalize, float norm_eps, float scale) {
-  extern __shared__ float route_smem[];            // per warp: E scores, then n_groups group scores
-  pdl_launch_dependents();
-  pdl_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= n_tokens) return;
-  float* s = route_smem + warp * (E + n_groups);
-  float* gs = s + E;
-  const float* z = logits + (size_t)t * E;
+// One token, by one warp: z its E logits (global or shared memory), s and gs scratch of E and n_groups floats,
+// ids and wts its `top` outputs.
+__device__ __forceinline__ void moe_route_token(const float* z, float* s, float* gs, int* __restrict__ ids,
+                                                float* __restrict__ wts, int lane, int E, int top, int n_groups,
+                                                int keep_groups, int group_top, int score_kind, int normalize,
+                                                float norm_eps, float scale) {
   if (score_kind == MOE_SCORE_SOFTMAX) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
@@ -107,9 +101,123 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int* __restri
   }
   if (lane < top) {
     const float w = normalize ? mine / (sum + norm_eps) : mine;
-    ids[(size_t)t * top + lane] = my_id;
-    wts[(size_t)t * top + lane] = w * scale;
+    ids[lane] = my_id;
+    wts[lane] = w * scale;
   }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
+                                 int n_tokens, int E, int top, int n_groups, int keep_groups, int group_top,
+                                 int score_kind, int normalize, float norm_eps, float scale) {
+  extern __shared__ float route_smem[];            // per warp: E scores, then n_groups group scores
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  float* s = route_smem + warp * (E + n_groups);
+  moe_route_token(logits + (size_t)t * E, s, s + E, ids + (size_t)t * top, wts + (size_t)t * top, lane, E, top, n_groups,
+                  keep_groups, group_top, score_kind, normalize, norm_eps, scale);
+}
+
+// The router's product and the routing in one kernel: a CTA of 8 warps takes TOK tokens (4 in a prompt step, so
+// that a row of the router's matrix is fetched once for four tokens; 1 in a step of few tokens, so that more SMs
+// take part); warp w computes the float32 logits of experts w, w + 8, ... (a lane adds its share of k in
+// ascending order, eight consecutive k at a time, then the lanes are added by a butterfly: the order depends on
+// nothing but K), then warp j routes token j.
+__device__ __forceinline__ void moe_load8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+__device__ __forceinline__ void moe_load8(const bf16* p, float* v) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x, v[2 * i + 1] = f.y;
+  }
+}
+
+template <typename TX, int TOK>
+__global__ void __launch_bounds__(256)
+moe_router_kernel(const TX* __restrict__ x, long long ldx, const float* __restrict__ w, int* __restrict__ ids,
+                  float* __restrict__ wts, int n_tokens, int K, int E, int top, int n_groups, int keep_groups,
+                  int group_top, int score_kind, int normalize, float norm_eps, float scale, int vec) {
+  extern __shared__ float route_smem[];            // per token: E logits, E scores, n_groups group scores
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t0 = blockIdx.x * TOK;
+  const int per_tok = 2 * E + n_groups;
+  const TX* xr[TOK];
+#pragma unroll
+  for (int j = 0; j < TOK; ++j) xr[j] = x + (size_t)min(t0 + j, n_tokens - 1) * ldx;
+  for (int e = warp; e < E; e += 8) {
+    const float* wr = w + (size_t)e * K;
+    float acc[TOK];
+#pragma unroll
+    for (int j = 0; j < TOK; ++j) acc[j] = 0.f;
+    if (vec) {           // K a multiple of 8 and rows 16-byte aligned: 8 consecutive k per lane and step
+#pragma unroll 2
+      for (int k = lane * 8; k < K; k += 256) {
+        float wv[8], xv[TOK][8];
+        moe_load8(wr + k, wv);
+#pragma unroll
+        for (int j = 0; j < TOK; ++j) moe_load8(xr[j] + k, xv[j]);
+#pragma unroll
+        for (int j = 0; j < TOK; ++j)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[j] = fmaf(xv[j][i], wv[i], acc[j]);
+      }
+    } else {
+      for (int k0 = lane * 8; k0 < K; k0 += 256)
+        for (int k = k0; k < k0 + 8 && k < K; ++k) {
+          const float wv = wr[k];
+#pragma unroll
+          for (int j = 0; j < TOK; ++j) acc[j] = fmaf(to_f32(xr[j][k]), wv, acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < TOK; ++j) {
+      const float v = warp_sum(acc[j]);
+      if (lane == 0) route_smem[j * per_tok + e] = v;
+    }
+  }
+  __syncthreads();
+  const int t = t0 + warp;
+  if (warp >= TOK || t >= n_tokens) return;
+  float* z = route_smem + warp * per_tok;
+  moe_route_token(z, z + E, z + 2 * E, ids + (size_t)t * top, wts + (size_t)t * top, lane, E, top, n_groups, keep_groups,
+                  group_top, score_kind, normalize, norm_eps, scale);
+}
+
+// x [T, K] (float32 or bfloat16, row stride ldx), w float32 [E, K] -> ids int32 [T, top], wts float32 [T, top].
+LLMX_API int llmx_moe_router(const void* x, int x_dtype, long long ldx, const float* w, int* ids, float* wts,
+                             int n_tokens, int K, int E, int top, int n_groups, int keep_groups, int group_top,
+                             int score_kind, int normalize, float norm_eps, float scale, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (K <= 0 || ldx < K || E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || n_groups <= 0 || E % n_groups ||
+      keep_groups <= 0 || keep_groups > n_groups || group_top <= 0 || group_top > 8 ||
+      top > E / n_groups * keep_groups)
+    return LLMX_REFUSED(1);
+  const int tok = n_tokens <= 64 ? 1 : 4;
+  const size_t smem = (size_t)tok * (2 * E + n_groups) * sizeof(float);
+  const dim3 grid((n_tokens + tok - 1) / tok);
+  const int esz = x_dtype == LLMX_F32 ? 4 : 2;
+  const int vec = (K % 8 == 0) && ((ldx * esz) % 16 == 0) && !((uintptr_t)x & 15) && !((uintptr_t)w & 15);
+#define GO(TX, TOK)                                                                                                    \
+  launch_pdl(moe_router_kernel<TX, TOK>, grid, dim3(256), smem, stream, (const TX*)x, ldx, w, ids, wts, n_tokens, K, E, \
+             top, n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale, vec)
+  if (x_dtype == LLMX_F32) {
+    if (tok == 1) GO(float, 1); else GO(float, 4);
+  } else if (x_dtype == LLMX_BF16) {
+    if (tok == 1) GO(bf16, 1); else GO(bf16, 4);
+  } else {
+    return LLMX_REFUSED(2);
+  }
+#undef GO
+  return LLMX_LAUNCH_STATUS();
 }
 
 LLMX_API int llmx_moe_route(const float* logits, int* ids, float* wts, int n_tokens, int E, int top, int n_groups,
@@ -132,8 +240,9 @@ LLMX_API int llmx_moe_route(const float* logits, int* ids, float* wts, int n_tok
 // number of rows); the used tiles come first, unused ones have expert -1.  max_tiles >= P / tile_rows + E.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ perm, int* __restrict__ tiles,
-                int max_tiles, int tile_rows) {
+moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ pair_weight, int P, int E, int top,
+                int n_tokens, int* __restrict__ perm, int* __restrict__ dest, float* __restrict__ sorted_weight,
+                int* __restrict__ tiles, int max_tiles, int tile_rows) {
   __shared__ int count[MOE_MAX_EXPERTS];
   __shared__ int start[MOE_MAX_EXPERTS + 1];
   __shared__ int tile0[MOE_MAX_EXPERTS + 1];
@@ -169,17 +278,26 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ per
   __syncthreads();
   for (int r = tid; r < P; r += blockDim.x) {
     const int e = ids[r];
-    perm[start[e] + atomicAdd(&count[e], 1)] = r;
+    const int place = start[e] + atomicAdd(&count[e], 1);
+    perm[place] = r;
+    if (dest) {             // where the pair's result goes in [top, n_tokens, ...], and its weight, in sorted order
+      const int t = r / top;
+      dest[place] = (r - t * top) * n_tokens + t;
+      sorted_weight[place] = pair_weight[r];
+    }
   }
 }
 
-LLMX_API int llmx_moe_sort(const int* ids, int P, int E, int* perm, int* tiles, int max_tiles, int tile_rows,
+// dest, sorted_weight (both [P]) may be null; with them pair_weight [P], top and n_tokens are needed.
+LLMX_API int llmx_moe_sort(const int* ids, const float* pair_weight, int P, int E, int top, int n_tokens, int* perm,
+                           int* dest, float* sorted_weight, int* tiles, int max_tiles, int tile_rows,
                            cudaStream_t stream) {
   if (P <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_EXPERTS || tile_rows <= 0 || max_tiles < (P + tile_rows - 1) / tile_rows + E)
     return LLMX_REFUSED(1);
-  launch_pdl(moe_sort_kernel, dim3(1), dim3(P >= 4096 ? 1024 : 256), 0, stream, ids, P, E, perm, tiles, max_tiles,
-             tile_rows);
+  if (dest && (!sorted_weight || !pair_weight || top <= 0 || n_tokens <= 0)) return LLMX_REFUSED(4);
+  launch_pdl(moe_sort_kernel, dim3(1), dim3(P >= 4096 ? 1024 : 256), 0, stream, ids, pair_weight, P, E, top, n_tokens,
+             perm, dest, sorted_weight, tiles, max_tiles, tile_rows);
   return LLMX_LAUNCH_STATUS();
 }
 

@@ -12,7 +12,7 @@
 // MMAs, four warps read the accumulators back (tcgen05.ld) and finish the unit:
 //
 //   MODE 1 (gate|up): two accumulators, rows n and n + F of the expert's [2F, K]; act[row, n] = silu(gate) * up
-//   MODE 0 (down):    y[choice][token][n] = weight[pair] * acc, pair = perm[row], float32
+//   MODE 0 (down):    y[dest[row]][n] = weight[row] * acc, float32 (dest = choice * tokens + token, from the sort)
 //
 // Which expert a unit reads is decided on the device by the kernel before, so every thread waits for that
 // kernel first.  Every wait on an mbarrier is bounded; when one runs out the CTA records it in the library's
@@ -33,9 +33,8 @@ __host__ __device__ constexpr uint32_t mt_idesc(int n) {     // bf16 x bf16 -> f
 template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(MT_THREADS)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                      TY* __restrict__ Y, const int* __restrict__ tiles, int max_tiles, const int* __restrict__ perm,
-                      const float* __restrict__ pair_weight, int top, int n_tokens, int N, int K, int w_rows,
-                      int n_stages, int row_tiles) {
+                      TY* __restrict__ Y, const int* __restrict__ tiles, int max_tiles, const int* __restrict__ dest,
+                      const float* __restrict__ sorted_weight, int N, int K, int w_rows, int n_stages, int row_tiles) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr uint32_t A_BYTES = MT_BM * MT_BK * 2;
@@ -53,9 +52,13 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages;
   const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
+  int* tile_dest = reinterpret_cast<int*>(bars + 2 * n_stages + 6);          // [BN] MODE 0: the unit's output rows
+  float* tile_weight = reinterpret_cast<float*>(tile_dest + BN);            // [BN] and their weights
+  volatile int* gave_up = reinterpret_cast<volatile int*>(tile_weight + BN); // an epilogue warp's wait ran out: all four leave
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
+    *gave_up = 0;
     for (int s = 0; s < n_stages; ++s) {
       mbar_init(full0 + 8u * s, 1);
       mbar_init(empty0 + 8u * s, 1);
@@ -155,9 +158,26 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       int e, row0, n_rows, n0;
       if (!unit(u, e, row0, n_rows, n0)) break;
       const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
+      if (MODE == 0) {
+        // where the unit's rows go and what they weigh: one coalesced load, shared by the four warps
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // (the unit before has been stored)
+        const int r = (int)threadIdx.x - 64;
+        if (r < BN && r < n_rows) {
+          tile_dest[r] = __ldcg(dest + row0 + r);
+          tile_weight[r] = __ldcg(sorted_weight + row0 + r);
+        }
+      }
       bool ok = mbar_wait(acc_full0 + 8u * buf, use & 1);
-      if (!ok && lane == 0) mt_report(3);
-      failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
+      if (!ok && lane == 0) {
+        mt_report(3);
+        *gave_up = 1;
+      }
+      if (MODE == 0) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // the rows' list is in place, and so is any warp's failure
+        failed = *gave_up != 0;
+      } else {
+        failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
+      }
       if (failed) break;
       tc_fence_after();
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
@@ -177,9 +197,7 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
               const float a = v[i];
               Y[(size_t)(row0 + r) * N + n] = from_f32<TY>(__fdividef(a, 1.0f + __expf(-a)) * g[i]);
             } else {
-              const int pr = __ldcg(perm + row0 + r);
-              const int t = pr / top, choice = pr - t * top;
-              Y[((size_t)choice * n_tokens + t) * N + n] = from_f32<TY>(__ldcg(pair_weight + pr) * v[i]);
+              Y[(size_t)tile_dest[r] * N + n] = from_f32<TY>(tile_weight[r] * v[i]);
             }
           }
         }
@@ -208,8 +226,8 @@ static int mt_sm_count() {
 }
 
 template <int BN, int MODE, typename TY>
-static int mt_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, const int* tiles, int max_tiles, const int* perm,
-                     const float* pair_weight, int top, int n_tokens, int N, int K, int w_rows, cudaStream_t stream) {
+static int mt_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, const int* tiles, int max_tiles, const int* dest,
+                     const float* sorted_weight, int N, int K, int w_rows, cudaStream_t stream) {
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr size_t STAGE = (size_t)N_ACC * MT_BM * MT_BK * 2 + (size_t)BN * MT_BK * 2;
   const int row_tiles = (N + MT_BM - 1) / MT_BM;
@@ -221,7 +239,7 @@ static int mt_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, cons
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
-  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8;
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 + (size_t)BN * 8 + 16;
   auto kernel = moe_grouped_tc_kernel<BN, MODE, TY>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -231,28 +249,29 @@ static int mt_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, cons
   }
   const int max_ctas = mt_sm_count() * ctas_per_sm;
   const int grid = n_units < max_ctas ? (int)n_units : max_ctas;
-  launch_pdl(kernel, dim3(grid), dim3(MT_THREADS), smem, stream, mw, mx, (TY*)Y, tiles, max_tiles, perm, pair_weight, top,
-             n_tokens, N, K, w_rows, stages, row_tiles);
+  launch_pdl(kernel, dim3(grid), dim3(MT_THREADS), smem, stream, mw, mx, (TY*)Y, tiles, max_tiles, dest, sorted_weight, N, K,
+             w_rows, stages, row_tiles);
   return LLMX_LAUNCH_STATUS();
 }
 
 // X: bf16 sorted rows [P, K] (row stride ldx); W: bf16 [E, w_rows, K] contiguous, w_rows = 2N when gated (gate rows,
 // then up rows) else N; tiles: int32 [max_tiles, 3] made with tile_rows rows per tile (16, 64 or 128).
-// gated: Y = act bf16 [P, N].  else: Y = float32 [top, n_tokens, N].
+// gated: Y = act bf16 [P, N].  else: Y = float32 rows of N, row dest[place] = sorted_weight[place] * product
+// (dest and sorted_weight [P] in sorted order, from the sort).
 LLMX_API int llmx_moe_grouped_tc(const void* X, long long ldx, long long P, const void* W, int n_experts, void* Y,
-                                 const int* tiles, int max_tiles, int tile_rows, const int* perm, const float* pair_weight,
-                                 int top, int n_tokens, int N, int K, int gated, cudaStream_t stream) {
-  if (P <= 0 || n_tokens <= 0) return 0;
-  if (N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || top <= 0 || max_tiles <= 0 ||
-      n_experts <= 0)
+                                 const int* tiles, int max_tiles, int tile_rows, const int* dest,
+                                 const float* sorted_weight, int N, int K, int gated, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || max_tiles <= 0 ||
+      n_experts <= 0 || (!gated && (!dest || !sorted_weight)))
     return LLMX_REFUSED(1);
   const int w_rows = gated ? 2 * N : N;
   CUtensorMap mw, mx;
   if (make_map(&mw, W, (uint64_t)n_experts * w_rows, (uint64_t)K, (uint64_t)K, MT_BM, true)) return LLMX_REFUSED(4);
   if (make_map(&mx, X, (uint64_t)P, (uint64_t)K, (uint64_t)ldx, (uint32_t)tile_rows, false)) return LLMX_REFUSED(4);
 #define GO(BN)                                                                                                      \
-  return gated ? mt_launch<BN, 1, bf16>(mw, mx, Y, tiles, max_tiles, perm, pair_weight, top, n_tokens, N, K, w_rows, stream) \
-               : mt_launch<BN, 0, float>(mw, mx, Y, tiles, max_tiles, perm, pair_weight, top, n_tokens, N, K, w_rows, stream)
+  return gated ? mt_launch<BN, 1, bf16>(mw, mx, Y, tiles, max_tiles, dest, sorted_weight, N, K, w_rows, stream) \
+               : mt_launch<BN, 0, float>(mw, mx, Y, tiles, max_tiles, dest, sorted_weight, N, K, w_rows, stream)
   switch (tile_rows) {
     case 16: GO(16);
     case 64: GO(64);

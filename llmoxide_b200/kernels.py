@@ -464,7 +464,7 @@ def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
-                         n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float) -> None:
+                         n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0) -> None:
     """Prompt attention on tcgen05, bfloat16, head size 128: q, out [T,H*128]
     packed sequence after sequence; the cache entry is [n_pages,G,64,128]."""
     _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
@@ -474,10 +474,10 @@ def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_p
         raise Unsupported("the tcgen05 prompt attention takes bfloat16 and head size 128")
     f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, q.shape[0], max_new, n_heads,
-             n_kv_heads, head_dim, int(window or 0), scale, _stream()), "attention_prefill_tc")
+             n_kv_heads, head_dim, int(window or 0), int(keep_first or 0), scale, _stream()), "attention_prefill_tc")
 
 
 def attention_prefill_tc_status(reset: bool = True) -> int:
@@ -628,26 +628,43 @@ def _split_view(proj):
     return 1, 0, proj.stride(0)
 
 
-def decay_scan(proj, out, state, seq_start, seq_past, seq_slot, decay, cos, sin, n_rot: int, activation: str,
-               k_scale: float, n_heads: int, head_dim: int, v_head_dim: int, q_off: int, k_off: int, v_off: int) -> None:
+def decay_scan(proj, out, state, seq_start, token_pos, seq_slot, decay, cos, sin, n_rot: int, activation: str,
+               k_scale: float, n_heads: int, head_dim: int, v_head_dim: int, q_off: int, k_off: int, v_off: int,
+               max_new: int = 0, seg_len: int = 0) -> None:
     """The recurrence S = decay_h S + k v^T, o = S^T q over every sequence's tokens of the step, in order.
     ``proj`` [T, N] (or split partials [S, T, N]) holds q heads at column ``q_off``, k heads at ``k_off``
     (``head_dim`` each) and v heads at ``v_off`` (``v_head_dim`` each); ``activation`` is applied to all three,
-    then q and k are rotated (first ``n_rot`` dims, float32 tables) and k is scaled.  ``out`` float32
-    [T, H*Dv]; ``state`` float32 [slots, H, D, Dv], read and written in place for the step's slots."""
-    _dev(proj, out, state, seq_start, seq_past, seq_slot, decay, cos, sin)
+    then q and k are rotated (first ``n_rot`` dims, float32 tables, at ``token_pos``) and k is scaled.  ``out`` float32
+    [T, H*Dv]; ``state`` float32 [slots, H, D, Dv], read and written in place for the step's slots.  A sequence
+    that brings more than ``seg_len`` tokens (0: 128) is walked in segments side by side; ``max_new`` is the most
+    tokens one sequence brings (0: not known, taken as all of them)."""
+    _dev(proj, out, state, seq_start, token_pos, seq_slot, decay, cos, sin)
     _contig("out", out), _contig("state", state)
     assert out.dtype == torch.float32 and state.dtype == torch.float32 and decay.dtype == torch.float32
     assert state.shape[1:] == (n_heads, head_dim, v_head_dim) and decay.numel() == n_heads
     n_split, split_stride, row_stride = _split_view(proj)
-    n_seqs = seq_past.numel()
+    n_seqs, T = seq_slot.numel(), out.shape[0]
+    pad4 = lambda n: (n + 3) // 4 * 4
+    # q, k and v of every (token, head) after activation, rotation and scale, float32, rows padded to 4 elements
+    prep = guard.scratch((T * n_heads * (2 * pad4(head_dim) + pad4(v_head_dim)),), torch.float32, out.device,
+                         "prepared q, k, v of the recurrence")
+    max_new = max_new if 0 < max_new <= T else T
+    seg = seg_len or 128
+    n_seg = (max_new + seg - 1) // seg
+    partial = None
+    if n_seg > 1:
+        partial = guard.scratch((n_seqs * n_heads * n_seg * head_dim * v_head_dim,), torch.float32, out.device,
+                                "last states of a prompt's segments")
     f = _fn("linear_attention", "llmx_decay_scan",
             [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(proj), _tag(proj), n_split, split_stride, row_stride, q_off, k_off, v_off, _ptr(out), _ptr(state),
-             _ptr(seq_start), _ptr(seq_past), _ptr(seq_slot), _ptr(decay), _ptr(cos), _ptr(sin), n_rot,
-             _ACTS[activation], k_scale, n_seqs, n_heads, head_dim, v_head_dim, n_sm(out.device), _stream()),
-           "decay_scan")
+             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), _tag(proj), n_split, split_stride, row_stride, q_off, k_off, v_off, _ptr(prep), _ptr(out),
+             _ptr(state), _ptr(partial), _ptr(seq_start), _ptr(token_pos), _ptr(seq_slot), _ptr(decay), _ptr(cos),
+             _ptr(sin), n_rot, _ACTS[activation], k_scale, T, n_seqs, max_new, seg, n_heads, head_dim, v_head_dim,
+             n_sm(out.device), _stream()), "decay_scan")
+    global launch_count
+    launch_count += 2 if n_seg > 1 else 1          # beside the preparation: the recurrence, and the segments' second pass
 
 
 def gated_norm(o, proj, g_off: int, gain, eps: float, gate: str, per_head: bool, y, n_heads: int,
@@ -690,14 +707,34 @@ def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int = MOE_TILE) -> in
     return (n_pairs + tile_rows - 1) // tile_rows + n_experts
 
 
-def moe_sort(ids, n_experts: int, perm, tiles, tile_rows: int = MOE_TILE) -> None:
+def moe_sort(ids, n_experts: int, perm, tiles, tile_rows: int = MOE_TILE, pair_weight=None, dest=None,
+             sorted_weight=None) -> None:
     """Orders the (token, choice) pairs by expert: ``perm`` int32 [P] (sorted place -> pair) and ``tiles``
-    int32 [max_tiles, 3] (expert or -1, first row, rows), of up to ``tile_rows`` rows each."""
-    _dev(ids, perm, tiles)
+    int32 [max_tiles, 3] (expert or -1, first row, rows), of up to ``tile_rows`` rows each.  With ``dest`` and
+    ``sorted_weight`` ([P]) also, in sorted order, the row choice * T + token where a pair's result goes and the
+    pair's weight (``pair_weight`` [T, top])."""
+    _dev(ids, perm, tiles, pair_weight, dest, sorted_weight)
     _contig("ids", ids), _contig("perm", perm), _contig("tiles", tiles)
-    f = _fn("moe", "llmx_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _check(f(_ptr(ids), ids.numel(), n_experts, _ptr(perm), _ptr(tiles), tiles.shape[0], tile_rows, _stream()),
-           "moe_sort")
+    T, top = ids.shape
+    f = _fn("moe", "llmx_moe_sort", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(pair_weight), ids.numel(), n_experts, top, T, _ptr(perm), _ptr(dest), _ptr(sorted_weight),
+             _ptr(tiles), tiles.shape[0], tile_rows, _stream()), "moe_sort")
+
+
+def moe_router(x, w, ids, weights, n_groups: int, keep_groups: int, group_top: int, score: str, normalize: bool,
+               norm_eps: float, scale: float) -> None:
+    """The router's product (float32 ``w`` [E, K] times the rows of ``x``, float32 sums) and the routing of
+    ``moe_route`` in one kernel."""
+    _dev(x, w, ids, weights)
+    _contig("w", w), _contig("ids", ids), _contig("weights", weights)
+    assert w.dtype == torch.float32 and x.stride(1) == 1 and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    T, top = ids.shape
+    f = _fn("moe", "llmx_moe_router",
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_float, c_float, c_void_p])
+    _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(w), _ptr(ids), _ptr(weights), T, x.shape[1], w.shape[0], top, n_groups,
+             keep_groups, group_top, _SCORES[score], int(normalize), norm_eps, scale, _stream()), "moe_router")
 
 
 def moe_tc_supports(x, w) -> bool:
@@ -715,11 +752,11 @@ def moe_gather_rows(x, perm, top: int, xs) -> None:
     _check(f(_ptr(x), x.stride(0), _ptr(perm), top, _ptr(xs), perm.numel(), x.shape[1], _stream()), "moe_gather_rows")
 
 
-def moe_grouped_tc(xs, w, y, perm, tiles, tile_rows: int, pair_weight, top: int, n_tokens: int, gated: bool) -> None:
+def moe_grouped_tc(xs, w, y, tiles, tile_rows: int, dest, sorted_weight, gated: bool) -> None:
     """The grouped products on tcgen05.  ``xs`` bfloat16 [P, K] in sorted order; ``gated``: w [E, 2F, K] (gate rows,
-    then up rows), y bfloat16 [P, F]; else w [E, N, K], y float32 [top, T, N] = weight of the pair times the product.
-    ``tiles`` made by ``moe_sort`` with ``tile_rows`` in (16, 64, 128)."""
-    _dev(xs, w, y, perm, tiles, pair_weight)
+    then up rows), y bfloat16 [P, F]; else w [E, N, K], y float32 [top, T, N] whose row ``dest[place]`` becomes
+    ``sorted_weight[place]`` times the product.  ``tiles`` made by ``moe_sort`` with ``tile_rows`` in (16, 64, 128)."""
+    _dev(xs, w, y, tiles, dest, sorted_weight)
     _contig("w", w), _contig("y", y)
     assert moe_tc_supports(xs, w) and tile_rows in (16, 64, 128)
     K = xs.shape[1]
@@ -727,15 +764,16 @@ def moe_grouped_tc(xs, w, y, perm, tiles, tile_rows: int, pair_weight, top: int,
     assert w.shape[2] == K and y.dtype == (torch.bfloat16 if gated else torch.float32)
     f = _fn("moe_tc", "llmx_moe_grouped_tc",
             [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_void_p])
     _check(f(_ptr(xs), xs.stride(0), xs.shape[0], _ptr(w), w.shape[0], _ptr(y), _ptr(tiles), tiles.shape[0], tile_rows,
-             _ptr(perm), _ptr(pair_weight), top, n_tokens, N, K, int(gated), _stream()), "moe_grouped_tc")
+             _ptr(dest), _ptr(sorted_weight), N, K, int(gated), _stream()), "moe_grouped_tc")
 
 
 def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gated: bool) -> None:
-    """Grouped products over the sorted pairs.  ``gated``: x [T, K] gathered through ``perm``, w [E, 2F, K]
-    (gate rows, then up rows), y [P, F] = silu(gate) * up in sorted order.  Else: x [P, K] in sorted order,
-    w [E, N, K], y float32 [top, T, N] = weight of the pair times the product."""
+    """Grouped products over the sorted pairs on the FMA units (the float32 path, and sizes the tensor-core kernel
+    does not take).  ``gated``: x [T, K] gathered through ``perm``, w [E, 2F, K] (gate rows, then up rows), y [P, F] =
+    silu(gate) * up in sorted order.  Else: x [P, K] in sorted order, w [E, N, K], y float32 [top, T, N] = weight of
+    the pair times the product.  ``tiles`` made by ``moe_sort`` with ``MOE_TILE`` rows per tile."""
     _dev(x, w, y, perm, tiles, pair_weight)
     _contig("w", w), _contig("y", y)
     assert x.stride(1) == 1 and x.dtype == w.dtype

@@ -85,8 +85,7 @@ class GQAttention:
             return libs | {"attention"}
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
             libs |= {"attention_decode",
-                     "attention_prefill_tc" if self.D == 128 and not self.keep_first else
-                     "attention_prefill" if self.D in (64, 128) else "attention"}
+                     "attention_prefill_tc" if self.D == 128 else "attention_prefill" if self.D == 64 else "attention"}
         else:
             libs.add("attention")
         return libs
@@ -125,18 +124,19 @@ class GQAttention:
     def attend(self, q, out, view, block_table, ctx):
         """bfloat16: the split-key kernel when every sequence brings one token;
         for prompts the tcgen05 kernel at head size 128 and the mma.sync tiled
-        kernel at head size 64 (and at 128 under a window that keeps its first
-        keys); the general kernel otherwise (values of another size than the
-        keys among them) and always in float32."""
+        kernel at head size 64; the general kernel otherwise (values of another
+        size than the keys among them) and always in float32.  All of them take
+        a window that keeps its first keys."""
         H, G, D = self.H, self.G, self.D
         fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
                 and self.rt.tensor_cores)
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
                                      self.scale, keep_first=self.keep_first)
-        elif fast and D == 128 and not self.keep_first:
+        elif fast and D == 128:
             kernels.attention_prefill_tc(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
-                                         ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale)
+                                         ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
+                                         keep_first=self.keep_first)
         elif fast and kernels.attention_prefill_supports(q, view.k, D):
             kernels.attention_prefill(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                       ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,

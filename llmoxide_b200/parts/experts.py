@@ -22,7 +22,6 @@ import torch
 
 from .. import kernels
 from ..errors import ConfigError, Unsupported
-from .linear import Linear
 from .registry import register_feed_forward
 
 
@@ -58,7 +57,7 @@ class RoutedExperts:
             raise Unsupported(f"{self.E} experts / top {self.top}: the routing kernel takes up to 1024 / 16")
         t = spec.tensors
         # the router decides in float32 whatever the compute dtype
-        self.router = Linear(weights.pop(t["router"].name).to(torch.float32).contiguous(), rt)
+        self.router = weights.pop(t["router"].name).to(torch.float32).contiguous()
         dt = rt.act_dtype
         gate_up = [torch.cat([weights.pop(t[f"gate{e}"].name), weights.pop(t[f"up{e}"].name)], dim=0).to(dt)
                    for e in range(self.E)]
@@ -71,7 +70,7 @@ class RoutedExperts:
                                  and self.F % 8 == 0)
 
     def libraries(self) -> set:
-        return {"moe"} | ({"moe_tc"} if self.tensor_cores else set()) | self.router.libraries()
+        return {"moe"} | ({"moe_tc"} if self.tensor_cores else set())
 
     def tile_rows(self, n_pairs: int) -> int:
         """Rows per tile of the grouped products: narrow tiles when an expert gets few rows (a decode step streams
@@ -82,24 +81,26 @@ class RoutedExperts:
     def forward(self, x, ctx, residual=None):
         T, dev = x.shape[0], x.device
         P = T * self.top
-        logits = self.router(x, out_dtype=torch.float32)
         ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         pair_w = torch.empty((T, self.top), dtype=torch.float32, device=dev)
-        kernels.moe_route(logits, ids, pair_w, self.top, self.n_groups, self.keep_groups, self.group_top, self.score,
-                          self.normalize, self.norm_eps, self.scale)
+        kernels.moe_router(x, self.router, ids, pair_w, self.n_groups, self.keep_groups, self.group_top, self.score,
+                           self.normalize, self.norm_eps, self.scale)
         perm = torch.empty((P,), dtype=torch.int32, device=dev)
         fast = self.tensor_cores and x.dtype == torch.bfloat16 and kernels.moe_tc_supports(x, self.gate_up)
         rows = self.tile_rows(P) if fast else kernels.MOE_TILE
         tiles = torch.empty((kernels.moe_max_tiles(P, self.E, rows), 3), dtype=torch.int32, device=dev)
-        kernels.moe_sort(ids, self.E, perm, tiles, rows)
         act = torch.empty((P, self.F), dtype=self.rt.act_dtype, device=dev)
         y = torch.empty((self.top, T, self.down.shape[1]), dtype=torch.float32, device=dev)
         if fast:
+            dest = torch.empty((P,), dtype=torch.int32, device=dev)
+            sorted_w = torch.empty((P,), dtype=torch.float32, device=dev)
+            kernels.moe_sort(ids, self.E, perm, tiles, rows, pair_w, dest, sorted_w)
             xs = torch.empty((P, x.shape[1]), dtype=torch.bfloat16, device=dev)
             kernels.moe_gather_rows(x, perm, self.top, xs)
-            kernels.moe_grouped_tc(xs, self.gate_up, act, perm, tiles, rows, pair_w, self.top, T, gated=True)
-            kernels.moe_grouped_tc(act, self.down, y, perm, tiles, rows, pair_w, self.top, T, gated=False)
+            kernels.moe_grouped_tc(xs, self.gate_up, act, tiles, rows, dest, sorted_w, gated=True)
+            kernels.moe_grouped_tc(act, self.down, y, tiles, rows, dest, sorted_w, gated=False)
         else:
+            kernels.moe_sort(ids, self.E, perm, tiles, rows)
             kernels.moe_grouped(x, self.gate_up, act, perm, tiles, pair_w, self.top, T, gated=True)
             kernels.moe_grouped(act, self.down, y, perm, tiles, pair_w, self.top, T, gated=False)
         return y

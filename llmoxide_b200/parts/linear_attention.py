@@ -74,8 +74,9 @@ class DecayLinearAttention:
         cos, sin, n_rot = tables if tables is not None else (None, None, 0)
         proj = self.qkvg(x, splits_ok=True)
         o = torch.empty((T, self.H * self.Dv), dtype=torch.float32, device=x.device)
-        kernels.decay_scan(proj, o, view.state, ctx.seq_start, ctx.seq_past, ctx.seq_slot, self.decay, cos, sin, n_rot,
-                           self.activation, self.k_scale, self.H, self.D, self.Dv, self.q_off, self.k_off, self.v_off)
+        kernels.decay_scan(proj, o, view.state, ctx.seq_start, ctx.token_pos, ctx.seq_slot, self.decay, cos, sin, n_rot,
+                           self.activation, self.k_scale, self.H, self.D, self.Dv, self.q_off, self.k_off, self.v_off,
+                           max_new=ctx.max_new)
         y = torch.empty((T, self.H * self.Dv), dtype=self.rt.act_dtype, device=x.device)
         kernels.gated_norm(o, proj, self.g_off, self.gain, self.eps, self.gate, self.per_head, y, self.H, self.Dv)
         return self.o(y, splits_ok=True)

@@ -155,7 +155,7 @@ def test_recurrence_norm_and_gate_against_the_plain_functions(H, D, Dv, n_rot, a
             o = plain.rms_norm(o.reshape(T, HDv), gain.double(), eps) * torch.sigmoid(g)
         return o
 
-    def run(cuts):
+    def run(cuts, seg_len=0):
         """cuts[i]: the portions sequence i arrives in; portion j of every sequence that still has one forms step j."""
         state = torch.zeros((4, H, D, Dv), dtype=torch.float32, device=DEV)
         slots = [2, 0, 3]
@@ -166,11 +166,12 @@ def test_recurrence_norm_and_gate_against_the_plain_functions(H, D, Dv, n_rot, a
             rows = torch.cat([projs[i][fed[i] : fed[i] + cuts[i][j]] for i in live]).to(dtype).to(DEV)
             counts = [cuts[i][j] for i in live]
             start = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
-            past = torch.tensor([fed[i] for i in live], dtype=torch.int32, device=DEV)
+            past = torch.tensor(np.concatenate([np.arange(fed[i], fed[i] + cuts[i][j]) for i in live]),
+                                dtype=torch.int32, device=DEV)             # every token's position
             slot = torch.tensor([slots[i] for i in live], dtype=torch.int32, device=DEV)
             o = torch.empty((rows.shape[0], HDv), dtype=torch.float32, device=DEV)
             kernels.decay_scan(rows, o, state, start, past, slot, torch.tensor(decay, device=DEV), cos, sin, n_rot, act,
-                               k_scale, H, D, Dv, 0, HD, 2 * HD)
+                               k_scale, H, D, Dv, 0, HD, 2 * HD, max_new=max(counts), seg_len=seg_len)
             y = torch.empty((rows.shape[0], HDv), dtype=dtype, device=DEV)
             kernels.gated_norm(o, rows, 2 * HD + HDv, None if gain is None else gain.to(DEV), eps, gate, per_head, y, H, Dv)
             at = 0
@@ -187,6 +188,11 @@ def test_recurrence_norm_and_gate_against_the_plain_functions(H, D, Dv, n_rot, a
     single = run([[1] * n for n in lens])
     for a, b, c in zip(whole, cut, single):
         assert torch.equal(a, b) and torch.equal(a, c)
+    # long prompts are walked in segments side by side and put together in a second pass: the same sums, rounded
+    # in another order (segments of 16 and of 24 tokens here; a later portion of a prompt in segments as well)
+    for seg_len, cuts in ((16, [[n] for n in lens]), (24, [[30, 7], [1], [5, 65]])):
+        for got, p in zip(run(cuts, seg_len), projs):
+            assert _rel(got.numpy(), plain_out(p).numpy()) < (2e-5 if dtype == torch.float32 else 1e-2)
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -487,3 +493,10 @@ def test_prompt_attention_with_kept_first_keys_equals_the_general_kernel(D, H, G
                               torch.tensor([L - n for L, n in zip(lens, new)], dtype=torch.int32, device=DEV),
                               len(lens), max(new), H, G, D, window, 0.7, keep_first=keep)
     assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2
+    if D == 128:            # the tcgen05 kernel of that head size
+        got = torch.empty_like(want)
+        kernels.attention_prefill_tc(qd, got, kd, vd, td, torch.tensor(start, device=DEV),
+                                     torch.tensor([L - n for L, n in zip(lens, new)], dtype=torch.int32, device=DEV),
+                                     len(lens), max(new), H, G, D, window, 0.7, keep_first=keep)
+        assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2
+        kernels.check_status()
