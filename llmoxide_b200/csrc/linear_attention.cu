@@ -210,26 +210,34 @@ decay_scan_kernel(const float* __restrict__ prep, float* __restrict__ out, float
       }
       return (acc0 + acc1) + (acc2 + acc3);
     };
-    auto finish = [&](int tt, float acc) {
+    const bool writer = r == 0 && col_live;
+    auto out_at = [&](int tt) { return out + (size_t)(t0 + base + tt) * H * Dv + (size_t)h * Dv + col; };
+    auto finish = [&](int tt, float acc, float before) {       // before: PASS 2, what the first pass left there
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      float* dst = out + (size_t)(t0 + base + tt) * H * Dv + (size_t)h * Dv + col;
       if (PASS == 1) {
-        if (r == 0 && col_live) *dst = acc;
+        if (writer) *out_at(tt) = acc;
       } else {
-        if (r == 0 && col_live) *dst += g_pow * acc;
+        if (writer) *out_at(tt) = before + g_pow * acc;
         g_pow *= g;
       }
     };
     if (n_tok == LA_CHUNK) {
-      float part[LA_CHUNK];
+      float part[LA_CHUNK], before[LA_CHUNK];
+      if (PASS == 2) {                       // the chunk's outputs of the first pass, fetched together
+#pragma unroll
+        for (int tt = 0; tt < LA_CHUNK; ++tt) before[tt] = writer ? __ldcg(out_at(tt)) : 0.f;
+      }
 #pragma unroll
       for (int tt = 0; tt < LA_CHUNK; ++tt) part[tt] = one_token(tt);
 #pragma unroll
-      for (int tt = 0; tt < LA_CHUNK; ++tt) finish(tt, part[tt]);
+      for (int tt = 0; tt < LA_CHUNK; ++tt) finish(tt, part[tt], PASS == 2 ? before[tt] : 0.f);
     } else {
-      for (int tt = 0; tt < n_tok; ++tt) finish(tt, one_token(tt));
+      for (int tt = 0; tt < n_tok; ++tt) {
+        const float before = (PASS == 2 && writer) ? __ldcg(out_at(tt)) : 0.f;
+        finish(tt, one_token(tt), before);
+      }
     }
     __syncthreads();                              // the buffer is refilled by the next round's copies
   }

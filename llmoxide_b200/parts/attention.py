@@ -45,9 +45,8 @@ class GQAttention:
         self.eps = float(spec.get("qk_norm_eps") or 0.0)
         if self.H % self.G:
             raise Unsupported(f"{self.H} heads are not a multiple of {self.G} kv heads")
-        self.plain = self.Dv == self.D                # the shape the tiled kernels are written for
-        if self.plain and (self.D % 16 or self.D > 256):
-            raise Unsupported(f"head_dim {self.D}: the attention kernels take multiples of 16 up to 256")
+        # the shape the tiled kernels are written for; every other one goes to the general kernel
+        self.plain = self.Dv == self.D and self.D % 16 == 0
         if max(self.D, self.Dv) > 256:
             raise Unsupported(f"head sizes {self.D}/{self.Dv}: the attention kernels take sizes up to 256")
         t = spec.tensors

@@ -66,7 +66,9 @@ class DecayLinearAttention:
     def libraries(self) -> set:
         return {"linear_attention"} | self.qkvg.libraries() | self.o.libraries()
 
-    def forward(self, x, ctx, view, writes_cache=True):
+    adds_to_residual = True      # forward() takes ``residual`` and may return None: "already added"
+
+    def forward(self, x, ctx, view, writes_cache=True, residual=None):
         if not writes_cache:
             raise Unsupported("a recurrent state has one writer: the layer that owns it")
         T = x.shape[0]
@@ -79,4 +81,6 @@ class DecayLinearAttention:
                            max_new=ctx.max_new)
         y = torch.empty((T, self.H * self.Dv), dtype=self.rt.act_dtype, device=x.device)
         kernels.gated_norm(o, proj, self.g_off, self.gain, self.eps, self.gate, self.per_head, y, self.H, self.Dv)
+        if residual is not None and self.o.add_into(y, residual):
+            return None
         return self.o(y, splits_ok=True)
