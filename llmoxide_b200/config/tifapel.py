@@ -5,8 +5,8 @@ config.json of this design is nested: ``vocab``, ``width``, ``norm.eps`` and a
 list ``layers``; every layer names its mixer (``type``: ``attention``,
 ``retention`` or ``lightning``) with the mixer's sizes (``mixer``) and its
 feed-forward (``mlp``: a routed mixture of experts, or null for none).  A
-layer is parallel: both sublayers read the one norm's output and their sum
-joins the residual stream.  Tensors: ``embed``, ``l<i>.norm1``,
+layer has a single norm that feeds mixer and feed-forward alike, and adds the
+two results to the residual stream together.  Tensors: ``embed``, ``l<i>.norm1``,
 ``l<i>.mix.*``, ``l<i>.mlp.*``, ``final.norm``, ``head``.
 
 An attention layer with ``kv_from: j`` has no key/value projections; it reads

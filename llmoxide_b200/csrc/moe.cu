@@ -19,10 +19,10 @@
 enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1 };
 
 // ---------------------------------------------------------------------------
-// Routing.  One warp per token.  scores s = sigmoid(z) (or softmax(z)); experts form n_groups equal groups of
-// neighbours; a group's score is the sum of its `group_top` largest scores; only experts of the `keep_groups`
-// best groups can be chosen; the `top` largest scores among them are chosen (ties: the lower index); weights
-// are the chosen scores, divided by their sum + norm_eps when `normalize`, times `scale`.
+// Routing.  One warp per token.  s = sigmoid(z) (or softmax(z)).  The expert indices are cut into n_groups
+// contiguous blocks of E / n_groups; a block ranks by the sum of its group_top highest s, and only the
+// keep_groups top-ranked blocks stay eligible.  Among the eligible experts the `top` highest s win (ties: the
+// lower index); a winner's weight is its s, over (the winners' sum + norm_eps) when `normalize`, times `scale`.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 #pragma unroll

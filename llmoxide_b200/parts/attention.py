@@ -11,8 +11,8 @@ query at position p sees keys first..p, first = 0 or p-(w-1) under a window
 
 Beyond the reference's layer: values may have a size of their own
 (``v_head_dim``); under a window the first ``keep_first`` keys of a sequence
-may stay visible (a position sees key j if j <= p and (p - j < window or
-j < keep_first)); a layer without key/value projections of its own
+may stay visible (from position p, key j is visible iff j <= p and either
+p - j < window or j < keep_first); a layer without key/value projections of its own
 (``own_kv`` false) only makes queries and reads the cache entry of the call
 that owns it, which then keeps what the widest of its readers can see
 (``cache_window``, ``cache_keep_first``).

@@ -97,7 +97,7 @@ def build_block(spec, weights: dict, rt):
 
 @register_arrangement("parallel")
 class ParallelBlock:
-    """One norm, and both sublayers read its output: x = norm(h); h += mixer(x) + feed_forward(x).  The mixer's
+    """A single norm feeds mixer and feed-forward: x = norm(h); h += mixer(x) + feed_forward(x).  The mixer's
     result joins the float32 stream at once (nothing else reads the stream before the next layer's norm, and the
     feed-forward reads x); the feed-forward's is handed on as the pending delta, which the next norm adds."""
 

@@ -2,12 +2,13 @@
 small gated layers, down(act(gate x) * (up x)), weighted by the router.
 
 Router logits z = W_r x are float32 (the router's matrix is kept in float32;
-x may be the compute dtype's rounding).  Scores are sigmoids of z (or a
-softmax over z).  With ``n_groups`` > 1 the experts form equal groups of
-neighbours, a group scores the sum of its ``group_score_top`` largest scores,
-and only experts of the ``keep_groups`` best groups can be chosen.  The
-chosen experts' scores, divided by their sum + ``normalize_eps`` when
-``normalize``, times ``scale``, weight the experts' outputs.
+x may be the compute dtype's rounding).  ``score``: s = sigmoid(z), or a
+softmax over z.  With ``n_groups`` > 1 the expert indices are cut into
+``n_groups`` contiguous blocks of equal length; every block is ranked by the
+sum of its ``group_score_top`` highest s, and a token's choice is restricted
+to the ``keep_groups`` top-ranked blocks.  The ``top`` highest s among the
+eligible experts are taken; their weights are those s, over (their sum +
+``normalize_eps``) when ``normalize``, times ``scale``.
 
 The step's (token, choice) pairs are ordered by expert on the device and the
 two products run grouped over that order (csrc/moe.cu), so nothing is read

@@ -152,8 +152,9 @@ def attention(h, w, p, m, k, v):
 
 
 def route(h, w_router, r):
-    """Per token: chosen experts and their weights.  Scores are sigmoids; experts form equal groups of
-    neighbours, a group scores the sum of its two best, only the best groups' experts can be chosen."""
+    """Per token: the picked experts and their weights.  s = sigmoid(logits); with groups, the expert axis is cut
+    into ``count`` equal contiguous blocks, a block ranks by the sum of its top-2 s, and picks are limited to the
+    ``keep`` top-ranked blocks."""
     s = torch.sigmoid(h @ w_router.T)                   # [T, E]
     T, E = s.shape
     allowed = torch.ones(T, E, dtype=torch.bool)
