@@ -155,17 +155,24 @@ decay_scan_kernel(const float* __restrict__ prep, float* __restrict__ out, float
 
   const int n_chunks = (n_new + LA_CHUNK - 1) / LA_CHUNK;
   const int qk_pieces = (PASS == 1 ? 2 : 1) * Dp / 4, v_pieces = PASS == 1 ? cols / 4 : 0, pieces = qk_pieces + v_pieces;
+  const int tid_tok = tid / pieces, tid_pc = tid - tid_tok * pieces;              // where this thread's first piece lies
+  const int step_tok = (int)blockDim.x / pieces, step_pc = (int)blockDim.x - step_tok * pieces;   // and its stride
   auto load_chunk = [&](int chunk) {
     float* buf = la_smem + (size_t)(chunk % LA_STAGES) * LA_CHUNK * tok_len;
     const int base = chunk * LA_CHUNK;
     const int n_tok = (n_new - base) < LA_CHUNK ? (n_new - base) : LA_CHUNK;
-    for (int tt = 0; tt < n_tok; ++tt) {
-      const float* src = prep + ((size_t)(t0 + base + tt) * H + h) * row_len;
+    // piece e of the chunk is piece (e % pieces) of token (e / pieces); a thread walks its pieces without dividing
+    const float* src0 = prep + ((size_t)(t0 + base) * H + h) * row_len;
+    const size_t tok_stride = (size_t)H * row_len;
+    int tt = tid_tok, pc = tid_pc;
+    for (int e = tid; e < n_tok * pieces; e += blockDim.x) {
+      const float* src = src0 + tt * tok_stride;
       float* dst = buf + tt * tok_len;
-      for (int pc = tid; pc < pieces; pc += blockDim.x) {
-        if (pc < qk_pieces) la_cp_async16(dst + 4 * pc, src + 4 * pc);
-        else if (c0 + 4 * (pc - qk_pieces) < Dvp) la_cp_async16(dst + 2 * Dp + 4 * (pc - qk_pieces), src + 2 * Dp + c0 + 4 * (pc - qk_pieces));
-      }
+      if (pc < qk_pieces) la_cp_async16(dst + 4 * pc, src + 4 * pc);
+      else if (c0 + 4 * (pc - qk_pieces) < Dvp) la_cp_async16(dst + 2 * Dp + 4 * (pc - qk_pieces), src + 2 * Dp + c0 + 4 * (pc - qk_pieces));
+      tt += step_tok;
+      pc += step_pc;
+      if (pc >= pieces) pc -= pieces, ++tt;
     }
   };
   for (int c = 0; c < LA_STAGES - 1; ++c) {
@@ -173,6 +180,8 @@ decay_scan_kernel(const float* __restrict__ prep, float* __restrict__ out, float
     la_cp_async_commit();
   }
   float g_pow = g;                                 // PASS 2: decay^(i+1) for the token at hand
+  const size_t out_stride = (size_t)H * Dv;
+  float* out_col = out + (size_t)t0 * out_stride + (size_t)h * Dv + col;        // this thread's column of the segment's first token
   for (int chunk = 0; chunk < n_chunks; ++chunk) {
     if (chunk + LA_STAGES - 1 < n_chunks) load_chunk(chunk + LA_STAGES - 1);     // into the buffer walked last round
     la_cp_async_commit();
@@ -211,7 +220,8 @@ decay_scan_kernel(const float* __restrict__ prep, float* __restrict__ out, float
       return (acc0 + acc1) + (acc2 + acc3);
     };
     const bool writer = r == 0 && col_live;
-    auto out_at = [&](int tt) { return out + (size_t)(t0 + base + tt) * H * Dv + (size_t)h * Dv + col; };
+    float* out_chunk = out_col + (size_t)base * out_stride;
+    auto out_at = [&](int tt) { return out_chunk + (size_t)tt * out_stride; };
     auto finish = [&](int tt, float acc, float before) {       // before: PASS 2, what the first pass left there
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
