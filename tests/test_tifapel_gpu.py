@@ -258,7 +258,7 @@ def test_one_key_stands_out_at_every_edge_of_the_mask(D, Dv, H, G, window, keep,
 # whole models
 # ---------------------------------------------------------------------------------------------------------
 
-LENGTHS = {"A": [5, 70, 1, 41, 150, 23], "B": [300, 7, 66, 131, 2, 200], "C": [260, 65, 1, 129]}
+LENGTHS = {"A": [5, 70, 1, 41, 150, 23], "B": [300, 7, 66, 131, 2, 200], "C": [260, 65, 1, 129], "D": [210, 33, 64, 1, 90]}
 
 
 @pytest.fixture(scope="module")
@@ -284,25 +284,37 @@ def _expected(folder, reqs):
 
 
 def _compare(got, want, dtype, what):
-    """float32: every position within rounding.  bfloat16: a token whose two best experts nearly tie may choose
-    the other one than the plain implementation does, so a few positions may lie outside the tolerance."""
+    """float32: every logit of every position within rounding (largest difference against the largest logit).
+    bfloat16: a position's error is the root mean square over the vocabulary of the difference (its mean taken
+    off) against that of the logits; a token whose best experts nearly tie may choose another one than the plain
+    implementation does, so a few positions may lie outside the tolerance."""
     worst, n, over = 0.0, 0, 0
     for rid in want:
         assert got[rid].shape == want[rid].shape, (what, rid)
-        scale = np.abs(want[rid]).max()
-        e = np.abs(got[rid] - want[rid]).max(axis=1) / scale
+        if dtype == "float32":
+            e = np.abs(got[rid] - want[rid]).max(axis=1) / np.abs(want[rid]).max()
+        else:
+            d = got[rid] - want[rid]
+            w = want[rid] - want[rid].mean(axis=1, keepdims=True)
+            e = (d - d.mean(axis=1, keepdims=True)).std(axis=1) / np.sqrt((w * w).mean())
         worst = max(worst, float(e.max()))
         n += len(e)
         over += int((e > (F32_TOL if dtype == "float32" else BF16_TOL)).sum())
     if dtype == "float32":
         assert over == 0, f"{what}: {over} of {n} positions differ from the plain implementation, worst {worst:.3e}"
     else:
-        assert over <= 0.05 * n and worst < 0.5, f"{what}: {over} of {n} positions beyond {BF16_TOL}, worst {worst:.3e}"
+        assert over <= max(2, 0.1 * n) and worst < 0.3, f"{what}: {over} of {n} positions beyond {BF16_TOL}, worst {worst:.3e}"
     return worst
 
 
+def _rms_err(got, want):
+    d = got - want
+    w = want - want.mean(axis=1, keepdims=True)
+    return (d - d.mean(axis=1, keepdims=True)).std(axis=1) / np.sqrt((w * w).mean())
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_cutting_matches_the_plain_implementation(folders, tmp_path, name, dtype):
     folder = folders[(name, dtype)]
     reqs = _requests(name)
@@ -332,7 +344,27 @@ def test_every_cutting_matches_the_plain_implementation(folders, tmp_path, name,
         for what, got in results.items():
             for rid in got:
                 assert ru.rel_err(got[rid], results["whole"][rid]) < 4e-6, (what, rid)
+    else:
+        # bfloat16, cutting against cutting: most tokens whose experts nearly tie choose alike under every cutting
+        # (a prompt step and a decode step round differently, so a few do not); a fault of the cache, the state
+        # or the batch would move every later position
+        for what, got in results.items():
+            e = np.concatenate([_rms_err(got[rid], results["whole"][rid]) for rid in got])
+            assert (e > BF16_TOL).sum() <= max(2, 0.05 * len(e)) and np.median(e) < 1.5e-2, \
+                (what, int((e > BF16_TOL).sum()), float(np.median(e)), float(e.max()))
     eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_as_a_user_runs_it(folders, tmp_path, dtype):
+    """``bin/trace_run`` as a subprocess on a Tifapel folder: unequal batches whose requests end at different steps,
+    with ``--max-tokens`` the bare sum of the live requests' tokens (the pages' padding is the runner's business)."""
+    folder = folders[("A", dtype)]
+    reqs = _requests("A")
+    steps = ru.trace_batches(reqs, 3, 0.6)
+    ru.run_trace_run(folder, dtype, steps, tmp_path / "out", max_tokens=sum(len(t) for t in reqs.values()))
+    got = ru.collect(steps, tmp_path / "out", ALL["A"]["vocab"])
+    _compare(got, _expected(folder, reqs), dtype, f"trace_run/{dtype}")
 
 
 def test_a_slot_used_again_starts_from_an_empty_state(folders):

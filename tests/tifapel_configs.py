@@ -59,7 +59,18 @@ TF_C = dict(
         _attention(4, 1, 128, 128, 0.09, mask=(100, 2), mlp=_moe(8, 2, 128, 1.0, groups=(2, 1))),
         _retention(2, 128, 64, [0.95, 0.999], rot=(128, 1000000.0), mlp=_moe(8, 2, 128, 1.0, groups=(2, 1))),
     ])
-ALL = {"A": TF_A, "B": TF_B, "C": TF_C}
+# Head sizes between the tiled kernels' (96: the decode kernel takes it, prompts go to the general kernel; 48 with
+# a rotation over 32 dims), as many key/value heads as heads, 20 experts in 5 blocks, a layer that keeps every block.
+TF_D = dict(
+    architecture="Tifapel", vocab=1000, width=192, norm=dict(eps=1e-6),
+    layers=[
+        _retention(4, 48, 96, [0.5, 0.9, 0.99, 0.9995], rot=(32, 10000.0), mlp=_moe(20, 3, 72, 1.2, groups=(5, 2))),
+        _attention(6, 2, 96, 96, 0.1, mask=(50, 5), mlp=_moe(20, 3, 72, 1.2, groups=(5, 2))),
+        _lightning(2, 64, 64, [0.97, 0.999], mlp=_moe(8, 1, 40, 1.0, groups=(4, 4))),
+        _attention(6, 2, 96, 96, 0.1, mask=(200, 0), kv_from=1, mlp=None),
+        _attention(8, 8, 32, 32, 0.18, mask=(30, 2), mlp=_moe(20, 3, 72, 1.2, groups=(5, 2))),
+    ])
+ALL = {"A": TF_A, "B": TF_B, "C": TF_C, "D": TF_D}
 
 
 def make_folder(tmp_path, name: str, dtype: str, seed: int = 4321):
