@@ -21,6 +21,10 @@ class RMSNorm:
 
     ROW_SCALE_MAX_TOKENS = 64      # what the products' epilogues take
 
+    def add(self, h, delta) -> None:
+        """h += delta (``delta`` [T,d] or split partials [S,T,d], added in order); nothing is normed."""
+        kernels.add_rms_norm(h, delta, self.gain, self.eps, None)
+
     def add_forward(self, h, delta, rows=None, write_h=True, out_dtype=None, row_scales_ok=False):
         """With ``row_scales_ok`` the caller's next products apply the norm's scale themselves; for a step of
         few tokens the result is then ``RowScaled`` (the norm in two halves, see ``parts.row_scaled``)."""

@@ -14,7 +14,8 @@ Interfaces (``rt`` is the ``Runtime``: device, compute dtype, limits):
 ``Norm(spec, weights, rt)``
     ``add_forward(h, delta, rows=None, write_h=True) -> x``: adds ``delta``
     (None, [T,d] or split partials [S,T,d]) to the float32 residual stream
-    ``h`` in place and returns the normalised rows in the compute dtype.
+    ``h`` in place and returns the normalised rows in the compute dtype;
+    ``add(h, delta)`` only adds (the ``parallel`` arrangement uses it).
 ``Position(spec, weights, rt)``
     ``rotary_tables() -> (cos, sin, n_rot)`` float32 [positions, n_rot/2], or
     ``None`` when the encoding does not rotate.
