@@ -4,12 +4,14 @@ description that the rest of the package reads."""
 from .qwen3 import Qwen3Config
 from .registry import architectures, config_class, read_config, register_architecture
 from .tifapel import TifapelConfig
+from .voserax import VoseraxConfig
 from .spec import BlockSpec, LayerCall, ModelSpec, PartSpec, TensorSpec, default_schedule
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
 register_architecture("Tifapel", TifapelConfig)
+register_architecture("Voserax", VoseraxConfig)
 
 __all__ = [
-    "Qwen3Config", "TifapelConfig", "architectures", "config_class", "read_config", "register_architecture",
+    "Qwen3Config", "TifapelConfig", "VoseraxConfig", "architectures", "config_class", "read_config", "register_architecture",
     "BlockSpec", "LayerCall", "ModelSpec", "PartSpec", "TensorSpec", "default_schedule",
 ]

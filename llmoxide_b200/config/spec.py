@@ -26,6 +26,9 @@ class TensorSpec:
     # "vector": gains and the like (float32 arithmetic whatever the storage);
     # "table": integer table (kept as int32).
     role: str = "matrix"
+    # (mean, standard deviation) of its random-weights values when the role's default does not suit it
+    # (a mixing matrix near the identity, a small correction); None: the role's.
+    init: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -54,6 +57,7 @@ class BlockSpec:
     feed_forward: PartSpec
     norms: Mapping[str, PartSpec]         # role in the arrangement -> norm
     position: Optional[PartSpec] = None   # position encoding handed to the mixer
+    params: Mapping[str, Any] = field(default_factory=dict)   # the arrangement's own constants
 
 
 @dataclass(frozen=True)
@@ -90,6 +94,9 @@ class ModelSpec:
     # Tensors a checkpoint may hold beyond the model's own, which are then left alone: exact names, or
     # "*suffix" for every name with that ending (buffers that exporters write beside the weights).
     ignored_tensors: tuple = ()
+    # Copies of the residual stream that the blocks' arrangement keeps (the stream is then [streams, T, d];
+    # the embedding fills every copy alike, and the final norm reads their sum).
+    residual_streams: int = 1
 
     def __post_init__(self):
         if isinstance(self.embedding, TensorSpec):

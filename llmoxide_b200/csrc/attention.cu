@@ -10,7 +10,8 @@
 // With `keep_first` > 0 the keys 0..keep_first-1 stay visible under the window
 // as well (they are taken first, then the window's keys).  Values may have a
 // size Dv of their own; a query row may sit in a wider row (q_stride elements
-// from token to token), e.g. the q|k|v row of a fused product.
+// from token to token), e.g. the q|k|v row of a fused product.  With `sink` > 0
+// the softmax's denominator has that much added: w_j = exp(s_j) / (sink + sum exp(s_j)).
 //
 // One warp per (token, head).  Keys are taken 32 at a time starting at the
 // range's first key: lane j scores key lo + c*32 + j with a sequential dot over
@@ -29,7 +30,7 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
                                        const int* __restrict__ block_table, int table_width,
                                        const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                                        int H, int G, int D, int Dv, size_t q_stride, int window, int keep_first,
-                                       float scale) {
+                                       float scale, float sink) {
   extern __shared__ float q_buf[];  // [ATT_WARPS][D]
   pdl_launch_dependents();
   pdl_wait();
@@ -87,7 +88,8 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
     m = m_new;
   }
   }
-  const float inv = 1.0f / l;
+  // a sink: `sink` keys of score 0 that have no value; they only add to the denominator
+  const float inv = 1.0f / (sink > 0.f ? l + sink * expf(-m) : l);
   TA* orow = out + ((size_t)t * H + hq) * Dv;
 #pragma unroll
   for (int i = 0; i < MAX_OWN; ++i) {
@@ -99,7 +101,7 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
 LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const void* k_cache,
                                   const void* v_cache, int cache_dtype, const int* block_table, int table_width,
                                   const int* token_seq, const int* token_pos, int n_tokens, int H, int G, int D,
-                                  int Dv, long long q_stride, int window, int keep_first, float scale,
+                                  int Dv, long long q_stride, int window, int keep_first, float scale, float sink,
                                   cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || D > ATT_MAX_D || window < 0) return LLMX_REFUSED(1);
@@ -109,7 +111,7 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
 #define CASE(TA, TC)                                                                                      \
   launch_pdl(attention_paged_kernel<TA, TC>, grid, dim3(ATT_WARPS * 32), smem, stream,                    \
       (const TA*)q, (TA*)out, (const TC*)k_cache, (const TC*)v_cache, block_table, table_width, token_seq, \
-      token_pos, H, G, D, Dv, (size_t)q_stride, window, keep_first, scale)
+      token_pos, H, G, D, Dv, (size_t)q_stride, window, keep_first, scale, sink)
   if (act_dtype == LLMX_F32 && cache_dtype == LLMX_F32) CASE(float, float);
   else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) CASE(bf16, bf16);
   else if (act_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) CASE(float, bf16);

@@ -44,6 +44,8 @@ LIBRARIES = {
     "linear_attention": (["linear_attention.cu"], []),
     "moe": (["moe.cu"], []),
     "moe_tc": (["moe_tc.cu"], []),
+    "short_conv": (["short_conv.cu"], []),
+    "stream_mix": (["stream_mix.cu"], []),
     "sampling": (["sampling.cu"], []),
     "random_init": (["random_init.cu"], []),
     # host code only (no CUDA): the cache's bookkeeping and the step plan

@@ -195,6 +195,31 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
 
+// Gated activations of the feed-forwards, act(g) * f(u):
+//   SILU            g sigmoid(g) * u
+//   RELU            max(g, 0) * u
+//   CLAMPED_SWISH   g' sigmoid(slope g') * (u' + shift),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
+enum { LLMX_ACT_SILU = 0, LLMX_ACT_RELU = 1, LLMX_ACT_CLAMPED_SWISH = 2 };
+struct GateAct {
+  int kind;
+  float slope, limit, shift;
+};
+__device__ __forceinline__ float gated_act(const GateAct a, float g, float u) {
+  if (a.kind == LLMX_ACT_SILU) return (g / (1.0f + expf(-g))) * u;
+  if (a.kind == LLMX_ACT_RELU) return fmaxf(g, 0.f) * u;
+  g = fminf(g, a.limit);
+  u = fminf(fmaxf(u, -a.limit), a.limit);
+  return (g / (1.0f + expf(-a.slope * g))) * (u + a.shift);
+}
+// The same with the fast exponential and division, for the epilogues of the bfloat16 tensor-core products.
+__device__ __forceinline__ float gated_act_fast(const GateAct a, float g, float u) {
+  if (a.kind == LLMX_ACT_SILU) return __fdividef(g, 1.0f + __expf(-g)) * u;
+  if (a.kind == LLMX_ACT_RELU) return fmaxf(g, 0.f) * u;
+  g = fminf(g, a.limit);
+  u = fminf(fmaxf(u, -a.limit), a.limit);
+  return __fdividef(g, 1.0f + __expf(-a.slope * g)) * (u + a.shift);
+}
+
 // Butterfly reductions: every lane ends with the same value, and the order of
 // the additions is fixed by the lane numbers alone.
 __device__ __forceinline__ float warp_sum(float v) {

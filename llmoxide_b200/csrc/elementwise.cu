@@ -66,6 +66,49 @@ LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, f
   return LLMX_LAUNCH_STATUS();
 }
 
+// The same with a learned position vector added (not scaled) and the row written to every one of n_streams
+// copies of the residual stream: h[s][t,:] = E[tok_t,:] * scale + P[pos_t,:], the sum in float32.
+template <typename TW>
+__global__ void embed_pos_kernel(const TW* __restrict__ table, const TW* __restrict__ pos_table,
+                                 const int* __restrict__ tokens, const int* __restrict__ token_pos,
+                                 float* __restrict__ h, size_t stream_stride, int n_streams, int d, int vocab,
+                                 int n_positions, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // never read outside the tables
+  const TW* row = table + (size_t)tok * d;
+  const TW* prow = nullptr;
+  if (pos_table) {
+    int p = token_pos[t];
+    p = p < 0 ? 0 : (p >= n_positions ? n_positions - 1 : p);
+    prow = pos_table + (size_t)p * d;
+  }
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = to_f32(row[i]) * scale;
+    if (prow) v += to_f32(prow[i]);
+    for (int s = 0; s < n_streams; ++s) h[(size_t)s * stream_stride + (size_t)t * d + i] = v;
+  }
+}
+
+LLMX_API int llmx_embed_pos(const void* table, const void* pos_table, int table_dtype, const int* tokens,
+                            const int* token_pos, float* h, long long stream_stride, int n_streams, int n_tokens, int d,
+                            int vocab, int n_positions, float scale, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (d <= 0 || vocab <= 0 || n_streams <= 0 || (pos_table && (n_positions <= 0 || !token_pos))) return LLMX_REFUSED(1);
+  const int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == LLMX_F32)
+    launch_pdl(embed_pos_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table,
+               (const float*)pos_table, tokens, token_pos, h, (size_t)stream_stride, n_streams, d, vocab, n_positions, scale);
+  else if (table_dtype == LLMX_BF16)
+    launch_pdl(embed_pos_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table,
+               (const bf16*)pos_table, tokens, token_pos, h, (size_t)stream_stride, n_streams, d, vocab, n_positions, scale);
+  else
+    return LLMX_REFUSED(2);
+  return LLMX_LAUNCH_STATUS();
+}
+
 // ---------------------------------------------------------------------------
 // Residual add + RMSNorm.  For output row r (source row t = rows ? rows[r] : r):
 //   v = h[t,:] + sum_s delta[s][t,:]      (partials added in the order s = 0..S-1)
@@ -630,12 +673,12 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
 }
 
 // ---------------------------------------------------------------------------
-// Gated activation: act[t,f] = silu(g) * u with g = sum_s gu[s][t,f] and
-// u = sum_s gu[s][t,F+f]; silu(x) = x / (1 + exp(-x)) in float32.
+// Gated activation: act[t,f] = gated_act(g, u) with g = sum_s gu[s][t,f] and
+// u = sum_s gu[s][t,F+f], in float32 (the kinds are listed in common.cuh; SiLU is x / (1 + exp(-x))).
 // ---------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void silu_gate_kernel(const TI* __restrict__ gu, int n_split, size_t split_stride,
-                                 TO* __restrict__ act, int n_tokens, int F, int block) {
+                                 TO* __restrict__ act, int n_tokens, int F, int block, const GateAct kind) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t n = (size_t)n_tokens * F;
@@ -651,20 +694,23 @@ __global__ void silu_gate_kernel(const TI* __restrict__ gu, int n_split, size_t 
       g += to_f32(p[s * split_stride + gcol]);
       u += to_f32(p[s * split_stride + ucol]);
     }
-    act[idx] = from_f32<TO>((g / (1.0f + expf(-g))) * u);
+    act[idx] = from_f32<TO>(gated_act(kind, g, u));
   }
 }
 
-LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
-                            int out_dtype, int n_tokens, int F, int block, cudaStream_t stream) {
+LLMX_API int llmx_gate_act(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
+                           int out_dtype, int n_tokens, int F, int block, int act_kind, float slope, float limit,
+                           float shift, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (F <= 0 || n_split < 1 || block < 0 || (block > 0 && F % block)) return LLMX_REFUSED(1);
+  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  const GateAct kind = {act_kind, slope, limit, shift};
   const size_t n = (size_t)n_tokens * F;
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
 #define CASE(TI, TO)                                                                                        \
   launch_pdl(silu_gate_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, n_split,      \
-             (size_t)split_stride, (TO*)act, n_tokens, F, block)
+             (size_t)split_stride, (TO*)act, n_tokens, F, block, kind)
   if (in_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
   else if (in_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
   else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);
@@ -672,6 +718,12 @@ LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long
   else return LLMX_REFUSED(2);
 #undef CASE
   return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
+                            int out_dtype, int n_tokens, int F, int block, cudaStream_t stream) {
+  return llmx_gate_act(gu, in_dtype, n_split, split_stride, act, out_dtype, n_tokens, F, block, LLMX_ACT_SILU, 1.f, 0.f,
+                       0.f, stream);
 }
 
 // ---------------------------------------------------------------------------

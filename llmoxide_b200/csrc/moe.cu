@@ -23,6 +23,8 @@ enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1 };
 // contiguous blocks of E / n_groups; a block ranks by the sum of its group_top highest s, and only the
 // keep_groups top-ranked blocks stay eligible.  Among the eligible experts the `top` highest s win (ties: the
 // lower index); a winner's weight is its s, over (the winners' sum + norm_eps) when `normalize`, times `scale`.
+// With a correction (`bias`, one number per expert) the groups are ranked and the experts chosen by s + bias,
+// while the weights stay the chosen experts' s.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 #pragma unroll
@@ -33,12 +35,12 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-// One token, by one warp: z its E logits (global or shared memory), s and gs scratch of E and n_groups floats,
-// ids and wts its `top` outputs.
-__device__ __forceinline__ void moe_route_token(const float* z, float* s, float* gs, int* __restrict__ ids,
+// One token, by one warp: z its E logits (global or shared memory), s, c and gs scratch of E, E and n_groups
+// floats (c: the scores the choice goes by), ids and wts its `top` outputs.
+__device__ __forceinline__ void moe_route_token(const float* z, float* s, float* c, float* gs, int* __restrict__ ids,
                                                 float* __restrict__ wts, int lane, int E, int top, int n_groups,
                                                 int keep_groups, int group_top, int score_kind, int normalize,
-                                                float norm_eps, float scale) {
+                                                float norm_eps, float scale, const float* __restrict__ bias) {
   if (score_kind == MOE_SCORE_SOFTMAX) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
@@ -50,6 +52,8 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
   } else {
     for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-z[e]));
   }
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) c[e] = bias ? s[e] + bias[e] : s[e];
   __syncwarp();
   const int per = E / n_groups;
   if (n_groups > 1 && keep_groups < n_groups) {
@@ -64,7 +68,7 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
         for (int e = g * per; e < (g + 1) * per; ++e) {
           bool used = false;
           for (int j = 0; j < k; ++j) used = used || picked[j] == e;
-          if (!used && s[e] > best) best = s[e], bi = e;
+          if (!used && c[e] > best) best = c[e], bi = e;
         }
         picked[k] = bi;
         sum += best;
@@ -83,7 +87,7 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
       __syncwarp();
     }
     for (int e = lane; e < E; e += 32)
-      if (gs[e / per] != -INFINITY) s[e] = -1.0f;   // not kept
+      if (gs[e / per] != -INFINITY) c[e] = -INFINITY;   // not kept
     __syncwarp();
   }
   float sum = 0.f, mine = 0.f;
@@ -92,12 +96,13 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32)
-      if (s[e] > best) best = s[e], bi = e;
+      if (c[e] > best) best = c[e], bi = e;
     warp_argmax(best, bi);
-    if (lane == 0) s[bi] = -2.0f;                   // chosen: out of the running
+    if (lane == 0) c[bi] = -INFINITY;               // chosen: out of the running
     __syncwarp();
-    if (lane == k) mine = best, my_id = bi;
-    sum += best;
+    const float sb = s[bi];
+    if (lane == k) mine = sb, my_id = bi;
+    sum += sb;
   }
   if (lane < top) {
     const float w = normalize ? mine / (sum + norm_eps) : mine;
@@ -108,23 +113,25 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
                                  int n_tokens, int E, int top, int n_groups, int keep_groups, int group_top,
-                                 int score_kind, int normalize, float norm_eps, float scale) {
-  extern __shared__ float route_smem[];            // per warp: E scores, then n_groups group scores
+                                 int score_kind, int normalize, float norm_eps, float scale,
+                                 const float* __restrict__ bias) {
+  extern __shared__ float route_smem[];            // per warp: E scores, E choice scores, n_groups group scores
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * 4 + warp;
   if (t >= n_tokens) return;
-  float* s = route_smem + warp * (E + n_groups);
-  moe_route_token(logits + (size_t)t * E, s, s + E, ids + (size_t)t * top, wts + (size_t)t * top, lane, E, top, n_groups,
-                  keep_groups, group_top, score_kind, normalize, norm_eps, scale);
+  float* s = route_smem + warp * (2 * E + n_groups);
+  moe_route_token(logits + (size_t)t * E, s, s + E, s + 2 * E, ids + (size_t)t * top, wts + (size_t)t * top, lane, E, top,
+                  n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale, bias);
 }
 
 // The router's product and the routing in one kernel: a CTA of 8 warps takes TOK tokens (4 in a prompt step, so
 // that a row of the router's matrix is fetched once for four tokens; 1 in a step of few tokens, so that more SMs
 // take part); warp w computes the float32 logits of experts w, w + 8, ... (a lane adds its share of k in
 // ascending order, eight consecutive k at a time, then the lanes are added by a butterfly: the order depends on
-// nothing but K), then warp j routes token j.
+// nothing but K), then warp j routes token j.  The matrix may hold n_extra rows behind the experts' (a gate
+// that reads the same input): their logits are written to extra_out [T, n_extra] as they are.
 __device__ __forceinline__ void moe_load8(const float* p, float* v) {
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
   v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
@@ -143,17 +150,19 @@ template <typename TX, int TOK>
 __global__ void __launch_bounds__(256)
 moe_router_kernel(const TX* __restrict__ x, long long ldx, const float* __restrict__ w, int* __restrict__ ids,
                   float* __restrict__ wts, int n_tokens, int K, int E, int top, int n_groups, int keep_groups,
-                  int group_top, int score_kind, int normalize, float norm_eps, float scale, int vec) {
-  extern __shared__ float route_smem[];            // per token: E logits, E scores, n_groups group scores
+                  int group_top, int score_kind, int normalize, float norm_eps, float scale, int vec,
+                  const float* __restrict__ bias, int n_extra, float* __restrict__ extra_out) {
+  extern __shared__ float route_smem[];            // per token: E + n_extra logits, E scores, n_groups group scores
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t0 = blockIdx.x * TOK;
-  const int per_tok = 2 * E + n_groups;
+  const int per_tok = 2 * E + n_extra + n_groups;
+  const int n_rows = E + n_extra;
   const TX* xr[TOK];
 #pragma unroll
   for (int j = 0; j < TOK; ++j) xr[j] = x + (size_t)min(t0 + j, n_tokens - 1) * ldx;
-  for (int e = warp; e < E; e += 8) {
+  for (int e = warp; e < n_rows; e += 8) {
     const float* wr = w + (size_t)e * K;
     float acc[TOK];
 #pragma unroll
@@ -188,27 +197,31 @@ moe_router_kernel(const TX* __restrict__ x, long long ldx, const float* __restri
   const int t = t0 + warp;
   if (warp >= TOK || t >= n_tokens) return;
   float* z = route_smem + warp * per_tok;
-  moe_route_token(z, z + E, z + 2 * E, ids + (size_t)t * top, wts + (size_t)t * top, lane, E, top, n_groups, keep_groups,
-                  group_top, score_kind, normalize, norm_eps, scale);
+  if (lane < n_extra) extra_out[(size_t)t * n_extra + lane] = z[E + lane];
+  // (the logits are not needed once the scores exist: their place holds the choice scores)
+  moe_route_token(z, z + n_rows, z, z + n_rows + E, ids + (size_t)t * top, wts + (size_t)t * top, lane, E, top, n_groups,
+                  keep_groups, group_top, score_kind, normalize, norm_eps, scale, bias);
 }
 
 // x [T, K] (float32 or bfloat16, row stride ldx), w float32 [E, K] -> ids int32 [T, top], wts float32 [T, top].
 LLMX_API int llmx_moe_router(const void* x, int x_dtype, long long ldx, const float* w, int* ids, float* wts,
                              int n_tokens, int K, int E, int top, int n_groups, int keep_groups, int group_top,
-                             int score_kind, int normalize, float norm_eps, float scale, cudaStream_t stream) {
+                             int score_kind, int normalize, float norm_eps, float scale, const float* bias,
+                             int n_extra, float* extra_out, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (n_extra < 0 || n_extra > 32 || (n_extra > 0 && !extra_out)) return LLMX_REFUSED(1);
   if (K <= 0 || ldx < K || E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || n_groups <= 0 || E % n_groups ||
       keep_groups <= 0 || keep_groups > n_groups || group_top <= 0 || group_top > 8 ||
       top > E / n_groups * keep_groups)
     return LLMX_REFUSED(1);
   const int tok = n_tokens <= 64 ? 1 : 4;
-  const size_t smem = (size_t)tok * (2 * E + n_groups) * sizeof(float);
+  const size_t smem = (size_t)tok * (2 * E + n_extra + n_groups) * sizeof(float);
   const dim3 grid((n_tokens + tok - 1) / tok);
   const int esz = x_dtype == LLMX_F32 ? 4 : 2;
   const int vec = (K % 8 == 0) && ((ldx * esz) % 16 == 0) && !((uintptr_t)x & 15) && !((uintptr_t)w & 15);
 #define GO(TX, TOK)                                                                                                    \
   launch_pdl(moe_router_kernel<TX, TOK>, grid, dim3(256), smem, stream, (const TX*)x, ldx, w, ids, wts, n_tokens, K, E, \
-             top, n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale, vec)
+             top, n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale, vec, bias, n_extra, extra_out)
   if (x_dtype == LLMX_F32) {
     if (tok == 1) GO(float, 1); else GO(float, 4);
   } else if (x_dtype == LLMX_BF16) {
@@ -222,15 +235,15 @@ LLMX_API int llmx_moe_router(const void* x, int x_dtype, long long ldx, const fl
 
 LLMX_API int llmx_moe_route(const float* logits, int* ids, float* wts, int n_tokens, int E, int top, int n_groups,
                             int keep_groups, int group_top, int score_kind, int normalize, float norm_eps,
-                            float scale, cudaStream_t stream) {
+                            float scale, const float* bias, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || top > 32 || n_groups <= 0 || E % n_groups ||
       keep_groups <= 0 || keep_groups > n_groups || group_top <= 0 || group_top > 8 ||
       top > E / n_groups * keep_groups)
     return LLMX_REFUSED(1);
-  const size_t smem = 4 * (size_t)(E + n_groups) * sizeof(float);
+  const size_t smem = 4 * (size_t)(2 * E + n_groups) * sizeof(float);
   launch_pdl(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), smem, stream, logits, ids, wts, n_tokens, E, top,
-             n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale);
+             n_groups, keep_groups, group_top, score_kind, normalize, norm_eps, scale, bias);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -238,11 +251,12 @@ LLMX_API int llmx_moe_route(const float* logits, int* ids, float* wts, int n_tok
 // Sort.  One CTA.  P = n_tokens * top pairs, pair r = t * top + choice.  Out: perm[P] (sorted place -> pair),
 // tiles: for every row tile of tile_rows sorted rows that lie in one expert's segment, (expert, first row,
 // number of rows); the used tiles come first, unused ones have expert -1.  max_tiles >= P / tile_rows + E.
+// Experts n_tiled..E-1 have no products (identity experts): their pairs are placed but get no tiles.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ pair_weight, int P, int E, int top,
                 int n_tokens, int* __restrict__ perm, int* __restrict__ dest, float* __restrict__ sorted_weight,
-                int* __restrict__ tiles, int max_tiles, int tile_rows) {
+                int* __restrict__ tiles, int max_tiles, int tile_rows, int n_tiled) {
   __shared__ int count[MOE_MAX_EXPERTS];
   __shared__ int start[MOE_MAX_EXPERTS + 1];
   __shared__ int tile0[MOE_MAX_EXPERTS + 1];
@@ -259,7 +273,7 @@ moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ pair_weig
       start[e] = at;
       tile0[e] = tl;
       at += count[e];
-      tl += (count[e] + tile_rows - 1) / tile_rows;
+      if (e < n_tiled) tl += (count[e] + tile_rows - 1) / tile_rows;
     }
     start[E] = at;
     tile0[E] = tl;
@@ -267,7 +281,7 @@ moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ pair_weig
   __syncthreads();
   for (int e = tid; e < E; e += blockDim.x) {
     const int n = count[e];
-    for (int k = 0, tl = tile0[e]; k < n; k += tile_rows, ++tl) {
+    for (int k = 0, tl = tile0[e]; k < n && e < n_tiled; k += tile_rows, ++tl) {
       tiles[3 * tl] = e;
       tiles[3 * tl + 1] = start[e] + k;
       tiles[3 * tl + 2] = (n - k) < tile_rows ? (n - k) : tile_rows;
@@ -290,14 +304,15 @@ moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ pair_weig
 
 // dest, sorted_weight (both [P]) may be null; with them pair_weight [P], top and n_tokens are needed.
 LLMX_API int llmx_moe_sort(const int* ids, const float* pair_weight, int P, int E, int top, int n_tokens, int* perm,
-                           int* dest, float* sorted_weight, int* tiles, int max_tiles, int tile_rows,
+                           int* dest, float* sorted_weight, int* tiles, int max_tiles, int tile_rows, int n_tiled,
                            cudaStream_t stream) {
   if (P <= 0) return 0;
+  if (n_tiled < 0 || n_tiled > E) return LLMX_REFUSED(1);
   if (E <= 0 || E > MOE_MAX_EXPERTS || tile_rows <= 0 || max_tiles < (P + tile_rows - 1) / tile_rows + E)
     return LLMX_REFUSED(1);
   if (dest && (!sorted_weight || !pair_weight || top <= 0 || n_tokens <= 0)) return LLMX_REFUSED(4);
   launch_pdl(moe_sort_kernel, dim3(1), dim3(P >= 4096 ? 1024 : 256), 0, stream, ids, pair_weight, P, E, top, n_tokens,
-             perm, dest, sorted_weight, tiles, max_tiles, tile_rows);
+             perm, dest, sorted_weight, tiles, max_tiles, tile_rows, n_tiled);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -305,7 +320,7 @@ LLMX_API int llmx_moe_sort(const int* ids, const float* pair_weight, int P, int 
 // Grouped products on the FMA units (float32 accumulation, k = 0..K-1 per output element).
 //
 // GATED: rows are tokens' rows of x gathered through perm (token = pair / top); W = [E][2F][K], gate rows then
-//   up rows; out act[place][f] = silu(gate) * up, in sorted order.
+//   up rows; out act[place][f] = gated_act(gate, up) (common.cuh), in sorted order.
 // else:  rows are act[place]; W = [E][N][K]; out y[choice][token][n] = weight[pair] * sum, float32: one partial
 //   per choice, which whoever adds them to the residual stream sums in the order of the choices.
 // ---------------------------------------------------------------------------
@@ -313,7 +328,7 @@ template <typename TX, typename TW, typename TY, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_grouped_fma_kernel(const TX* __restrict__ X, long long ldx, const TW* __restrict__ W, TY* __restrict__ Y,
                        const int* __restrict__ perm, const int* __restrict__ tiles,
-                       const float* __restrict__ pair_weight, int top, int n_tokens, int N, int K) {
+                       const float* __restrict__ pair_weight, int top, int n_tokens, int N, int K, const GateAct act) {
   __shared__ float Xs[MOE_BK][MOE_TILE + 4];
   __shared__ float Ws[MOE_BK][MOE_TILE + 4];
   __shared__ float Us[GATED ? MOE_BK : 1][MOE_TILE + 4];
@@ -386,8 +401,7 @@ moe_grouped_fma_kernel(const TX* __restrict__ X, long long ldx, const TW* __rest
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       if constexpr (GATED) {
-        const float g = acc[i][j];
-        Y[(size_t)(row0 + lr) * N + n] = from_f32<TY>(g / (1.0f + expf(-g)) * acu[i][j]);
+        Y[(size_t)(row0 + lr) * N + n] = from_f32<TY>(gated_act(act, acc[i][j], acu[i][j]));
       } else {
         const int t = pr / top, choice = pr - t * top;
         Y[((size_t)choice * n_tokens + t) * N + n] = from_f32<TY>(pair_weight[pr] * acc[i][j]);
@@ -402,14 +416,16 @@ moe_grouped_fma_kernel(const TX* __restrict__ X, long long ldx, const TW* __rest
 LLMX_API int llmx_moe_grouped_fma(const void* X, int x_dtype, long long ldx, const void* W, int w_dtype, void* Y,
                                   int y_dtype, const int* perm, const int* tiles, int max_tiles,
                                   const float* pair_weight, int top, int n_tokens, int N, int K, int gated,
-                                  cudaStream_t stream) {
+                                  int act_kind, float slope, float limit, float shift, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  const GateAct act = {act_kind, slope, limit, shift};
   if (N <= 0 || K <= 0 || top <= 0 || max_tiles <= 0 || max_tiles > 65535 || ldx < K) return LLMX_REFUSED(1);
   if (x_dtype != w_dtype) return LLMX_REFUSED(2);
   dim3 grid((N + MOE_TILE - 1) / MOE_TILE, max_tiles);
 #define GO(TX, TY, G)                                                                                          \
   launch_pdl(moe_grouped_fma_kernel<TX, TX, TY, G>, grid, dim3(256), 0, stream, (const TX*)X, ldx, (const TX*)W, \
-             (TY*)Y, perm, tiles, pair_weight, top, n_tokens, N, K)
+             (TY*)Y, perm, tiles, pair_weight, top, n_tokens, N, K, act)
   if (gated) {
     if (x_dtype == LLMX_F32 && y_dtype == LLMX_F32) GO(float, float, true);
     else if (x_dtype == LLMX_BF16 && y_dtype == LLMX_BF16) GO(bf16, bf16, true);
@@ -421,5 +437,71 @@ LLMX_API int llmx_moe_grouped_fma(const void* X, int x_dtype, long long ldx, con
     else return LLMX_REFUSED(2);
   }
 #undef GO
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Identity experts and a gated shared expert, both written as further partials of the feed-forward's result.
+//
+// identity: for every pair (t, choice) whose expert id is >= n_real, y[choice][t][:] = weight * x[t][:] (the
+//   expert's output is its input).  One CTA per pair; pairs of real experts are left alone.
+// row_gate: out[t][:] = gate(z[t * ldz]) * sum_p in[p][t][:], gate = sigmoid: the shared expert's result times one
+//   number per token.
+// ---------------------------------------------------------------------------
+template <typename TX>
+__global__ void moe_identity_kernel(const TX* __restrict__ x, long long ldx, const int* __restrict__ ids,
+                                    const float* __restrict__ wts, float* __restrict__ y, int n_tokens, int top, int d,
+                                    int n_real) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  if (ids[pair] < n_real) return;
+  const int t = pair / top, choice = pair - t * top;
+  const float w = wts[pair];
+  const TX* xr = x + (size_t)t * ldx;
+  float* yr = y + ((size_t)choice * n_tokens + t) * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) yr[i] = w * to_f32(xr[i]);
+}
+
+LLMX_API int llmx_moe_identity(const void* x, int x_dtype, long long ldx, const int* ids, const float* wts, float* y,
+                               int n_tokens, int top, int d, int n_real, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (top <= 0 || d <= 0 || ldx < d) return LLMX_REFUSED(1);
+  const dim3 grid((unsigned)n_tokens * top);
+  if (x_dtype == LLMX_F32)
+    launch_pdl(moe_identity_kernel<float>, grid, dim3(128), 0, stream, (const float*)x, ldx, ids, wts, y, n_tokens, top, d, n_real);
+  else if (x_dtype == LLMX_BF16)
+    launch_pdl(moe_identity_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)x, ldx, ids, wts, y, n_tokens, top, d, n_real);
+  else
+    return LLMX_REFUSED(2);
+  return LLMX_LAUNCH_STATUS();
+}
+
+template <typename TI>
+__global__ void moe_row_gate_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, const float* __restrict__ z,
+                                    int ldz, float* __restrict__ out, int n_tokens, int d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float gate = 1.0f / (1.0f + expf(-z[(size_t)t * ldz]));
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = 0.f;
+    for (int p = 0; p < n_split; ++p) v += to_f32(in[(size_t)p * split_stride + (size_t)t * d + i]);
+    out[(size_t)t * d + i] = gate * v;
+  }
+}
+
+LLMX_API int llmx_moe_row_gate(const void* in, int in_dtype, int n_split, long long split_stride, const float* z, int ldz,
+                               float* out, int n_tokens, int d, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (d <= 0 || n_split < 1 || ldz < 1) return LLMX_REFUSED(1);
+  if (in_dtype == LLMX_F32)
+    launch_pdl(moe_row_gate_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)in, n_split,
+               (size_t)split_stride, z, ldz, out, n_tokens, d);
+  else if (in_dtype == LLMX_BF16)
+    launch_pdl(moe_row_gate_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const bf16*)in, n_split,
+               (size_t)split_stride, z, ldz, out, n_tokens, d);
+  else
+    return LLMX_REFUSED(2);
   return LLMX_LAUNCH_STATUS();
 }

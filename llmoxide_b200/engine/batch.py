@@ -72,6 +72,8 @@ class StepContext:
     block_tables: list
     widths: tuple
     probe: object = None     # callable(name, tensor) for named intermediates of the step, or None
+    # what one layer call leaves for later calls of the same step (by name): an earlier layer's values, say
+    carry: dict = field(default_factory=dict)
 
 
 N_FIXED = 7        # arrays before the block tables: tokens, token_seq, token_pos, seq_start, seq_past, seq_slot, want_rows

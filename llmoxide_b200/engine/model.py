@@ -71,11 +71,18 @@ class DecoderModel:
     def forward(self, ctx, cache: Cache) -> torch.Tensor:
         """float32 logits [n_want, vocab] at ``ctx.want_rows``."""
         d = self.spec.hidden_size
-        h = torch.empty((ctx.n_tokens, d), dtype=torch.float32, device=self.rt.device)
-        self.embedding.forward(ctx.tokens, h)
+        S = int(getattr(self.spec, "residual_streams", 1) or 1)
+        # the residual stream, or S copies of it where the blocks' arrangement keeps several
+        h = torch.empty((ctx.n_tokens, d) if S == 1 else (S, ctx.n_tokens, d), dtype=torch.float32, device=self.rt.device)
+        if getattr(self.embedding, "needs_context", False):
+            self.embedding.forward(ctx.tokens, h, ctx)
+        else:
+            self.embedding.forward(ctx.tokens, h if S == 1 else h[0])
+            if S > 1:
+                h[1:].copy_(h[:1].expand(S - 1, -1, -1))
         probe = ctx.probe
         if probe:
-            probe("model.input_embed", h)
+            probe("model.input_embed", h if S == 1 else h[0])
         pending = None
         for i, call in enumerate(self.spec.schedule):
             if probe:
@@ -86,9 +93,12 @@ class DecoderModel:
         ctx.probe = probe
         if probe:
             if pending is not None:
-                kernels.add_rms_norm(h, pending, self.final_norm.gain, self.final_norm.eps, None)  # h += the last delta
+                if hasattr(self.final_norm, "add"):
+                    self.final_norm.add(h, pending)      # h += the last delta
+                else:
+                    kernels.add_rms_norm(h, pending, self.final_norm.gain, self.final_norm.eps, None)
                 pending = None
-            probe(f"l_out-{len(self.spec.schedule) - 1}", h)
+            probe(f"l_out-{len(self.spec.schedule) - 1}", h if S == 1 else h.sum(0))
         n_want = ctx.want_rows.numel()
         if n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)

@@ -224,6 +224,101 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: f
              table.shape[0], scale, _stream()), "embed")
 
 
+def embed_positions(table, positions, tokens, token_pos, h, scale: float = 1.0) -> None:
+    """h[s][t,:] = float32(table[tokens[t],:]) * scale + float32(positions[token_pos[t],:]) for every copy s of the
+    residual stream; h float32 [T,d] or [S,T,d]; ``positions`` None or a table of the same dtype and width."""
+    _dev(table, positions, tokens, token_pos, h)
+    _contig("table", table), _contig("h", h)
+    assert tokens.dtype == torch.int32 and h.dtype == torch.float32
+    if positions is not None:
+        _contig("positions", positions)
+        assert positions.dtype == table.dtype and positions.shape[1] == table.shape[1] and token_pos.dtype == torch.int32
+    n_streams, stride = (h.shape[0], h.stride(0)) if h.dim() == 3 else (1, 0)
+    f = _fn("elementwise", "llmx_embed_pos",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
+             c_void_p])
+    _check(f(_ptr(table), _ptr(positions), _tag(table), _ptr(tokens), _ptr(token_pos), _ptr(h), stride, n_streams,
+             tokens.numel(), table.shape[1], table.shape[0], 0 if positions is None else positions.shape[0], scale,
+             _stream()), "embed_positions")
+
+
+def stream_mix_norm(h, delta, mix, write, read, gain, eps: float, out, rows=None, write_h: bool = True) -> None:
+    """Copies of the residual stream h float32 [S,T,d].  First the update a sublayer owes, when ``mix`` is given:
+    h_r <- sum_s mix[s,r] h_s + write[r] * delta (``delta`` None, [T,d] or split partials [P,T,d] added in order;
+    the copies are stored when ``write_h``).  Then out[r] = rmsnorm(sum_s read[s] h_s)[rows[r]] * gain (``read``
+    None: the plain sum; ``out`` None: only the update)."""
+    _dev(h, delta, mix, write, read, gain, out, rows)
+    _contig("h", h)
+    assert h.dtype == torch.float32 and h.dim() == 3
+    S, T, d = h.shape
+    n_split, stride, dtag = 1, 0, F32
+    if delta is not None:
+        _contig("delta", delta)
+        if delta.dim() == 2:
+            delta = delta.unsqueeze(0)
+        assert delta.shape[1:] == (T, d), (delta.shape, h.shape)
+        n_split, stride, dtag = delta.shape[0], delta.stride(0), _tag(delta)
+    for w, n in ((mix, S * S), (write, S), (read, S)):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == n and w.is_contiguous())
+    n_rows = T if rows is None else rows.numel()
+    if out is not None:
+        _contig("out", out)
+        assert out.shape[0] >= n_rows and out.shape[-1] == d and gain.dtype == torch.float32
+    f = _fn("stream_mix", "llmx_stream_mix_norm",
+            [c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), h.stride(0), S, _ptr(delta), dtag, n_split, stride, _ptr(mix), _ptr(write), _ptr(read), _ptr(rows),
+             n_rows, _ptr(gain), eps, _ptr(out), _tag(out) if out is not None else F32, d, int(write_h), _stream()),
+           "stream_mix_norm")
+
+
+def conv_rope_cache(proj, state, conv_w, taps: int, q_out, k_cache, v_cache, block_table, ctx, cos, sin, n_rot: int,
+                    v_first, v_lambda, v_mix_mode: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                    v_head_dim: int) -> None:
+    """A short causal convolution (``conv_w`` float32 [C, taps]; taps 0: none) over the fused q|k|v projection
+    ``proj`` ([T,C] or float32 partials [P,T,C]) with the sequences' earlier rows from ``state`` float32
+    [slots, taps-1, C]; then q and k rotated (q to ``q_out`` [T,H*D], k to the cache) and v written to the cache:
+    as it is (``v_mix_mode`` 0), also copied to ``v_first`` float32 [T,G*Dv] (1), or mixed with it as
+    (1 - l) v + l v_first, l = ``v_lambda[0]`` (2).  ``ctx``: the step's index arrays."""
+    _dev(proj, state, conv_w, q_out, k_cache, v_cache, block_table, cos, sin, v_first, v_lambda)
+    _contig("proj", proj), _contig("q_out", q_out), _contig("block_table", block_table)
+    n_split, stride = (proj.shape[0], proj.stride(0)) if proj.dim() == 3 else (1, 0)
+    T = proj.shape[-2]
+    C = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
+    assert proj.shape[-1] == C and q_out.shape == (T, n_heads * head_dim)
+    assert k_cache.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    if taps:
+        assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and conv_w.is_contiguous()
+    if taps > 1:
+        assert state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C) and state.is_contiguous()
+    if v_mix_mode:
+        assert v_first.dtype == torch.float32 and v_first.shape == (T, n_kv_heads * v_head_dim) and v_first.is_contiguous()
+    f = _fn("short_conv", "llmx_conv_rope_cache",
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), _tag(proj), n_split, stride, _ptr(state), _ptr(conv_w), taps, _ptr(q_out), _tag(q_out),
+             _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table), block_table.shape[1], _ptr(ctx.token_seq),
+             _ptr(ctx.token_pos), _ptr(ctx.seq_start), _ptr(ctx.seq_past), _ptr(ctx.seq_slot), _ptr(cos), _ptr(sin), n_rot,
+             _ptr(v_first), _ptr(v_lambda), v_mix_mode, T, n_heads, n_kv_heads, head_dim, v_head_dim, _stream()),
+           "conv_rope_cache")
+
+
+def conv_state_update(proj, state, taps: int, ctx) -> None:
+    """Moves the convolution's state on by the step's tokens: afterwards ``state[slot]`` holds the projected rows
+    of every sequence's last taps-1 positions."""
+    if taps <= 1:
+        return
+    _dev(proj, state)
+    n_split, stride = (proj.shape[0], proj.stride(0)) if proj.dim() == 3 else (1, 0)
+    C = proj.shape[-1]
+    assert state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C) and state.is_contiguous()
+    f = _fn("short_conv", "llmx_conv_state_update",
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(proj), _tag(proj), n_split, stride, _ptr(state), taps, _ptr(ctx.seq_start), _ptr(ctx.seq_slot),
+             ctx.n_seqs, C, _stream()), "conv_state_update")
+
+
 def softcap(x: torch.Tensor, cap: float) -> None:
     """x = cap * tanh(x / cap) in place; x float32, contiguous."""
     _dev(x)
@@ -318,9 +413,21 @@ def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, tok
              v_head_dim, int(write_cache), _stream()), "qk_norm_rope_cache")
 
 
-def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
-    """gu [S,T,2F] or [T,2F] -> out [T,F] = silu(gate) * up.  ``block`` = 0:
-    gate columns, then up columns; ``block`` > 0: blocks of that many gate
+GATE_ACTS = {"silu": 0, "relu": 1, "clamped_swish": 2}
+
+
+def gate_act_args(activation="silu") -> tuple:
+    """(kind, slope, limit, shift) as the kernels take them.  ``activation``: "silu", "relu", or
+    ("clamped_swish", slope, limit, shift): min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, +-limit) + shift)."""
+    if isinstance(activation, str):
+        return GATE_ACTS[activation], 1.0, 0.0, 0.0
+    name, slope, limit, shift = activation
+    return GATE_ACTS[name], float(slope), float(limit), float(shift)
+
+
+def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0, activation="silu") -> None:
+    """gu [S,T,2F] or [T,2F] -> out [T,F] = act(gate) * up (SiLU unless ``activation`` says otherwise, see
+    ``gate_act_args``).  ``block`` = 0: gate columns, then up columns; ``block`` > 0: blocks of that many gate
     columns each followed by the up columns of the same features."""
     _dev(gu, out)
     _contig("gu", gu), _contig("out", out)
@@ -328,9 +435,11 @@ def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
         gu = gu.unsqueeze(0)
     S, T, F2 = gu.shape
     assert out.shape == (T, F2 // 2)
-    f = _fn("elementwise", "llmx_silu_gate",
-            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(gu), _tag(gu), S, gu.stride(0), _ptr(out), _tag(out), T, F2 // 2, block, _stream()), "silu_gate")
+    f = _fn("elementwise", "llmx_gate_act",
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float,
+             c_void_p])
+    _check(f(_ptr(gu), _tag(gu), S, gu.stride(0), _ptr(out), _tag(out), T, F2 // 2, block, *gate_act_args(activation),
+             _stream()), "gate_act")
 
 
 def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
@@ -345,9 +454,11 @@ def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos, n_heads: int,
-                    n_kv_heads: int, head_dim: int, window, scale: float, v_head_dim=None, keep_first: int = 0) -> None:
+                    n_kv_heads: int, head_dim: int, window, scale: float, v_head_dim=None, keep_first: int = 0,
+                    sink: float = 0.0) -> None:
     """General attention over the paged cache; q [T,H*D] (rows may be the first columns of wider rows), out
-    [T,H*Dv].  Under a window the first ``keep_first`` keys of a sequence stay visible."""
+    [T,H*Dv].  Under a window the first ``keep_first`` keys of a sequence stay visible.  ``sink`` is added to the
+    softmax's denominator (as many keys of score 0 that have no value)."""
     _dev(q, out, k_cache, v_cache, block_table, token_seq, token_pos)
     _contig("out", out), _contig("block_table", block_table)
     v_head_dim = v_head_dim or head_dim
@@ -358,10 +469,11 @@ def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos,
         raise Unsupported(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
     f = _fn("attention", "llmx_attention_paged",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _tag(q), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
              block_table.shape[1], _ptr(token_seq), _ptr(token_pos), q.shape[0], n_heads, n_kv_heads, head_dim,
-             v_head_dim, q.stride(0), int(window or 0), int(keep_first or 0), scale, _stream()), "attention_paged")
+             v_head_dim, q.stride(0), int(window or 0), int(keep_first or 0), scale, float(sink or 0.0), _stream()),
+           "attention_paged")
 
 
 def n_sm(device=None) -> int:
@@ -512,8 +624,13 @@ def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def gemm_tc_gated_supports(activation) -> bool:
+    """Whether the tensor-core product applies this gated activation in its epilogue."""
+    return activation == "silu"
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1, gated=False,
-            pair: bool = False, scale=None, accumulate: bool = False) -> None:
+            pair: bool = False, scale=None, accumulate: bool = False, activation="silu") -> None:
     """bfloat16 x [T,K] times w [N,K]^T on tcgen05.  ``out`` is [T,N] (bfloat16
     or float32), or float32 partials [n_split,T,N] of a split reduction, or,
     with ``gated``, [T,N/2] = silu(gate) * up: ``gated=True`` (or 1) for
@@ -530,6 +647,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
     T, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.is_contiguous()
+    if gated and not gemm_tc_gated_supports(activation):
+        raise Unsupported(f"the tensor-core product has no epilogue for the activation {activation!r}")
     if gated:
         assert n_split == 1 and out.shape == (T, N // 2)
         ldy, stride = N // 2, 0
@@ -689,18 +808,20 @@ _SCORES = {"sigmoid": 0, "softmax": 1}
 
 
 def moe_route(logits, ids, weights, top: int, n_groups: int, keep_groups: int, group_top: int, score: str,
-              normalize: bool, norm_eps: float, scale: float) -> None:
+              normalize: bool, norm_eps: float, scale: float, bias=None) -> None:
     """Per token (row of float32 ``logits`` [T, E]): its ``top`` experts (``ids`` int32 [T, top]) and their
-    weights (float32 [T, top]); see moe.cu for the rule."""
-    _dev(logits, ids, weights)
+    weights (float32 [T, top]); see moe.cu for the rule.  ``bias`` float32 [E]: a correction added to the scores
+    for the choice only."""
+    _dev(logits, ids, weights, bias)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == logits.shape[1] and bias.is_contiguous())
     _contig("logits", logits), _contig("ids", ids), _contig("weights", weights)
     assert logits.dtype == torch.float32 and ids.dtype == torch.int32 and weights.dtype == torch.float32
     T, E = logits.shape
     f = _fn("moe", "llmx_moe_route",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-             c_void_p])
+             c_void_p, c_void_p])
     _check(f(_ptr(logits), _ptr(ids), _ptr(weights), T, E, top, n_groups, keep_groups, group_top, _SCORES[score],
-             int(normalize), norm_eps, scale, _stream()), "moe_route")
+             int(normalize), norm_eps, scale, _ptr(bias), _stream()), "moe_route")
 
 
 def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int = MOE_TILE) -> int:
@@ -708,39 +829,49 @@ def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int = MOE_TILE) -> in
 
 
 def moe_sort(ids, n_experts: int, perm, tiles, tile_rows: int = MOE_TILE, pair_weight=None, dest=None,
-             sorted_weight=None) -> None:
+             sorted_weight=None, n_tiled=None) -> None:
     """Orders the (token, choice) pairs by expert: ``perm`` int32 [P] (sorted place -> pair) and ``tiles``
     int32 [max_tiles, 3] (expert or -1, first row, rows), of up to ``tile_rows`` rows each.  With ``dest`` and
     ``sorted_weight`` ([P]) also, in sorted order, the row choice * T + token where a pair's result goes and the
-    pair's weight (``pair_weight`` [T, top])."""
+    pair's weight (``pair_weight`` [T, top]).  Experts from ``n_tiled`` on (identity experts) get no tiles."""
     _dev(ids, perm, tiles, pair_weight, dest, sorted_weight)
     _contig("ids", ids), _contig("perm", perm), _contig("tiles", tiles)
     T, top = ids.shape
     f = _fn("moe", "llmx_moe_sort", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_int, c_int, c_void_p])
+                                     c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(ids), _ptr(pair_weight), ids.numel(), n_experts, top, T, _ptr(perm), _ptr(dest), _ptr(sorted_weight),
-             _ptr(tiles), tiles.shape[0], tile_rows, _stream()), "moe_sort")
+             _ptr(tiles), tiles.shape[0], tile_rows, n_experts if n_tiled is None else n_tiled, _stream()), "moe_sort")
 
 
 def moe_router(x, w, ids, weights, n_groups: int, keep_groups: int, group_top: int, score: str, normalize: bool,
-               norm_eps: float, scale: float) -> None:
+               norm_eps: float, scale: float, bias=None, extra_out=None) -> None:
     """The router's product (float32 ``w`` [E, K] times the rows of ``x``, float32 sums) and the routing of
-    ``moe_route`` in one kernel."""
-    _dev(x, w, ids, weights)
+    ``moe_route`` in one kernel.  With ``extra_out`` float32 [T, n], ``w`` holds n more rows behind the experts',
+    whose products are written there as they are."""
+    _dev(x, w, ids, weights, bias, extra_out)
+    n_extra = 0 if extra_out is None else extra_out.shape[1]
+    assert extra_out is None or (extra_out.dtype == torch.float32 and extra_out.is_contiguous())
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == w.shape[0] - n_extra and bias.is_contiguous())
     _contig("w", w), _contig("ids", ids), _contig("weights", weights)
     assert w.dtype == torch.float32 and x.stride(1) == 1 and ids.dtype == torch.int32 and weights.dtype == torch.float32
     T, top = ids.shape
     f = _fn("moe", "llmx_moe_router",
             [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_float, c_float, c_void_p])
-    _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(w), _ptr(ids), _ptr(weights), T, x.shape[1], w.shape[0], top, n_groups,
-             keep_groups, group_top, _SCORES[score], int(normalize), norm_eps, scale, _stream()), "moe_router")
+             c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(w), _ptr(ids), _ptr(weights), T, x.shape[1], w.shape[0] - n_extra, top,
+             n_groups, keep_groups, group_top, _SCORES[score], int(normalize), norm_eps, scale, _ptr(bias), n_extra,
+             _ptr(extra_out), _stream()), "moe_router")
 
 
 def moe_tc_supports(x, w) -> bool:
     """Shapes the tensor-core grouped product takes: bfloat16, K a multiple of 8, 16-byte aligned rows."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def moe_tc_gated_supports(activation) -> bool:
+    """Whether the tensor-core grouped product applies this gated activation in its epilogue."""
+    return activation == "silu"
 
 
 def moe_gather_rows(x, perm, top: int, xs) -> None:
@@ -752,13 +883,13 @@ def moe_gather_rows(x, perm, top: int, xs) -> None:
     _check(f(_ptr(x), x.stride(0), _ptr(perm), top, _ptr(xs), perm.numel(), x.shape[1], _stream()), "moe_gather_rows")
 
 
-def moe_grouped_tc(xs, w, y, tiles, tile_rows: int, dest, sorted_weight, gated: bool) -> None:
+def moe_grouped_tc(xs, w, y, tiles, tile_rows: int, dest, sorted_weight, gated: bool, activation="silu") -> None:
     """The grouped products on tcgen05.  ``xs`` bfloat16 [P, K] in sorted order; ``gated``: w [E, 2F, K] (gate rows,
     then up rows), y bfloat16 [P, F]; else w [E, N, K], y float32 [top, T, N] whose row ``dest[place]`` becomes
     ``sorted_weight[place]`` times the product.  ``tiles`` made by ``moe_sort`` with ``tile_rows`` in (16, 64, 128)."""
     _dev(xs, w, y, tiles, dest, sorted_weight)
     _contig("w", w), _contig("y", y)
-    assert moe_tc_supports(xs, w) and tile_rows in (16, 64, 128)
+    assert moe_tc_supports(xs, w) and tile_rows in (16, 64, 128) and (not gated or moe_tc_gated_supports(activation))
     K = xs.shape[1]
     N = w.shape[1] // 2 if gated else w.shape[1]
     assert w.shape[2] == K and y.dtype == (torch.bfloat16 if gated else torch.float32)
@@ -769,7 +900,7 @@ def moe_grouped_tc(xs, w, y, tiles, tile_rows: int, dest, sorted_weight, gated: 
              _ptr(dest), _ptr(sorted_weight), N, K, int(gated), _stream()), "moe_grouped_tc")
 
 
-def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gated: bool) -> None:
+def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gated: bool, activation="silu") -> None:
     """Grouped products over the sorted pairs on the FMA units (the float32 path, and sizes the tensor-core kernel
     does not take).  ``gated``: x [T, K] gathered through ``perm``, w [E, 2F, K] (gate rows, then up rows), y [P, F] =
     silu(gate) * up in sorted order.  Else: x [P, K] in sorted order, w [E, N, K], y float32 [top, T, N] = weight of
@@ -782,6 +913,34 @@ def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gate
     assert w.shape[2] == K
     f = _fn("moe", "llmx_moe_grouped_fma",
             [c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
     _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(w), _tag(w), _ptr(y), _tag(y), _ptr(perm), _ptr(tiles), tiles.shape[0],
-             _ptr(pair_weight), top, n_tokens, N, K, int(gated), _stream()), "moe_grouped")
+             _ptr(pair_weight), top, n_tokens, N, K, int(gated), *gate_act_args(activation), _stream()), "moe_grouped")
+
+
+def moe_identity(x, ids, weights, y, n_real: int) -> None:
+    """y[choice, t, :] = weights[t, choice] * x[t, :] for every pair whose expert id is ``n_real`` or more (an
+    identity expert's output is its input); the other pairs' rows are left alone.  y float32 [top, T, d]."""
+    _dev(x, ids, weights, y)
+    _contig("ids", ids), _contig("weights", weights), _contig("y", y)
+    T, top = ids.shape
+    assert x.stride(1) == 1 and y.dtype == torch.float32 and y.shape[-2:] == (T, x.shape[1]) and y.shape[0] >= top
+    f = _fn("moe", "llmx_moe_identity",
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(ids), _ptr(weights), _ptr(y), T, top, x.shape[1], n_real, _stream()),
+           "moe_identity")
+
+
+def moe_row_gate(parts, z, out) -> None:
+    """out[t, :] = sigmoid(z[t]) * sum_p parts[p, t, :]; ``parts`` [T, d] or partials [P, T, d]; ``z`` float32, one
+    number per token (a column of a wider row: its stride is taken); ``out`` float32 [T, d]."""
+    _dev(parts, z, out)
+    _contig("parts", parts), _contig("out", out)
+    if parts.dim() == 2:
+        parts = parts.unsqueeze(0)
+    assert out.dtype == torch.float32 and parts.shape[1:] == out.shape and z.dtype == torch.float32
+    assert z.dim() == 1 and z.numel() == out.shape[0]
+    f = _fn("moe", "llmx_moe_row_gate",
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(parts), _tag(parts), parts.shape[0], parts.stride(0), _ptr(z), z.stride(0), _ptr(out), out.shape[0],
+             out.shape[1], _stream()), "moe_row_gate")

@@ -16,6 +16,17 @@ p - j < window or j < keep_first); a layer without key/value projections of its 
 (``own_kv`` false) only makes queries and reads the cache entry of the call
 that owns it, which then keeps what the widest of its readers can see
 (``cache_window``, ``cache_keep_first``).
+
+Three more options, each a parameter.  ``conv_taps`` n > 0: a short causal
+convolution over time on every channel of q, k and v, directly after the
+projection (tensors ``q_conv``, ``k_conv``, ``v_conv`` [channels, n], no bias:
+y_p = sum_j w[:, j] u_(p - n + 1 + j), zeros before the sequence's start); the
+last n - 1 projected rows of a sequence are per-sequence state.  ``sink`` s > 0:
+the softmax's denominator has s added, w_j = exp(s_j) / (s + sum_j exp(s_j)) (a
+sink of score 0 that has no value).  ``v_mix``: "source" leaves this call's
+values (after the convolution) for later calls of the step under the name
+``v_mix_key``; "mix" replaces its values by (1 - l) v + l v_source with the
+learned scalar l (tensor ``v_mix``) before they are cached.
 """
 
 from __future__ import annotations
@@ -23,7 +34,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from ..cache import KVNeed
+from ..cache import KVNeed, StateNeed
 from ..errors import Unsupported
 from .linear import Linear
 from .registry import register_mixer
@@ -68,10 +79,28 @@ class GQAttention:
             self.q_gain = weights.pop(t["q_norm"].name).to(torch.float32).contiguous()
             self.k_gain = weights.pop(t["k_norm"].name).to(torch.float32).contiguous()
         self.position = position
+        self.taps = int(spec.get("conv_taps") or 0)
+        self.sink = float(spec.get("sink") or 0.0)
+        self.v_mix, self.v_mix_key = spec.get("v_mix"), spec.get("v_mix_key", "v_mix")
+        if self.v_mix not in (None, "source", "mix"):
+            raise Unsupported(f"v_mix {self.v_mix!r}: 'source' or 'mix'")
+        self.conv_w = self.v_lambda = None
+        if self.taps:
+            if not self.own_kv or self.q_gain is not None:
+                raise Unsupported("the short convolution is built for a layer with its own keys and values and no q/k norm")
+            self.conv_w = torch.cat([weights.pop(t[r].name).to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")],
+                                    dim=0).contiguous()
+        if self.v_mix:
+            lam = weights.pop(t["v_mix"].name).to(torch.float32).reshape(1).contiguous()
+            self.v_lambda = lam if self.v_mix == "mix" else None      # the source's own weight is unused
+        # the projection's rows go through the convolution kernel (which also rotates, mixes and writes the cache)
+        self.staged = bool(self.taps or self.v_mix)
+        self.channels = (self.H + self.G) * self.D + self.G * self.Dv
 
     def cache_need(self):
+        state = StateNeed((self.taps - 1, self.channels)) if self.taps > 1 else None
         return KVNeed(self.G, self.D, self.cache_window, v_head_dim=None if self.Dv == self.D else self.Dv,
-                      keep_first=self.cache_keep_first), None
+                      keep_first=self.cache_keep_first), state
 
     @property
     def takes_row_scales(self) -> bool:
@@ -80,7 +109,9 @@ class GQAttention:
 
     def libraries(self) -> set:
         libs = {"elementwise"} | self.q_only.libraries() | self.o.libraries()
-        if not self.plain:
+        if self.staged:
+            libs.add("short_conv")
+        if not self.plain or self.sink:
             return libs | {"attention"}
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
             libs |= {"attention_decode",
@@ -100,7 +131,21 @@ class GQAttention:
         block_table = ctx.block_tables[view.group]
         if writes_cache and not self.own_kv:
             raise Unsupported("a layer without key/value projections cannot write a cache entry")
-        if not writes_cache and self.q_gain is None and n_rot == 0:
+        if self.staged:
+            if not writes_cache:
+                raise Unsupported("a layer with a short convolution or mixed values owns its cache entry")
+            qkv = self.qkv(x, splits_ok=True)
+            q = torch.empty((T, H * D), dtype=self.rt.act_dtype, device=dev)
+            v_first, mode = None, 0
+            if self.v_mix == "source":
+                v_first = ctx.carry[self.v_mix_key] = torch.empty((T, G * Dv), dtype=torch.float32, device=dev)
+                mode = 1
+            elif self.v_mix == "mix":
+                v_first, mode = ctx.carry[self.v_mix_key], 2
+            kernels.conv_rope_cache(qkv, view.state, self.conv_w, self.taps, q, view.k, view.v, block_table, ctx, cos, sin,
+                                    n_rot, v_first, self.v_lambda, mode, H, G, D, Dv)
+            kernels.conv_state_update(qkv, view.state, self.taps, ctx)
+        elif not writes_cache and self.q_gain is None and n_rot == 0:
             # A call that reads another call's cache entry makes only queries; nothing is done to them.
             q = self.q_only(x, out_dtype=self.rt.act_dtype)
         else:
@@ -128,7 +173,7 @@ class GQAttention:
         a window that keeps its first keys."""
         H, G, D = self.H, self.G, self.D
         fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
-                and self.rt.tensor_cores)
+                and self.rt.tensor_cores and not self.sink)
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
                                      self.scale, keep_first=self.keep_first)
@@ -142,4 +187,5 @@ class GQAttention:
                                       keep_first=self.keep_first)
         else:
             kernels.attention_paged(q, out, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
-                                    H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first)
+                                    H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first,
+                                    sink=self.sink)

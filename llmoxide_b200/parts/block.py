@@ -137,3 +137,66 @@ class ParallelBlock:
                 return a
             self.norm.add(h, a)
         return out
+
+
+@register_arrangement("hyper_connections")
+class HyperConnectionBlock:
+    """Pre-norm sublayers over ``streams`` copies of the residual stream (h [S,T,d], float32).  Sublayer q reads
+    u = sum_s in_q[s] h_s through its norm; its result y joins the copies as
+    h_r <- sum_s mix_q[s,r] h_s + residual_mult * out_q[r] * y, every copy from the old ones.  The weights ride
+    with the sublayer's norm (``parts.norm``); the update is owed to the next norm, whose kernel applies it while it
+    reads the copies, so a layer is two norm kernels beside its mixer and feed-forward as in ``pre_norm``.  With one
+    copy and no connection weights this is h += residual_mult * sublayer(norm(h))."""
+
+    def __init__(self, spec, weights: dict, rt):
+        position = None
+        if spec.position is not None:
+            position = rt_shared_position(spec.position, weights, rt)
+        self.streams = int(spec.params.get("streams", 1))
+        mult = float(spec.params.get("residual_mult", 1.0))
+        self.mixer_norm = build_part(NORMS, "norm", _with_mult(spec.norms["mixer"], mult), weights, rt)
+        self.mixer = lookup(MIXERS, "mixer", spec.mixer.kind)(spec.mixer, position, weights, rt)
+        self.feed_forward = build_part(FEED_FORWARDS, "feed-forward", spec.feed_forward, weights, rt)
+        self.ff_norm = None
+        if "feed_forward" in spec.norms:
+            self.ff_norm = build_part(NORMS, "norm", _with_mult(spec.norms["feed_forward"], mult), weights, rt)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def libraries(self) -> set:
+        libs = set()
+        for part in (self.mixer_norm, self.ff_norm, self.mixer, self.feed_forward):
+            if part is not None:
+                libs |= getattr(part, "libraries", set)()
+        return libs
+
+    def forward(self, h, pending, ctx, view, writes_cache=True):
+        if h.dim() == 2:
+            h = h.unsqueeze(0)
+        S = h.shape[0]
+        probe = getattr(ctx, "probe", None)
+        if probe:
+            self.mixer_norm.add(h, pending)
+            pending = None
+            probe("resid_in", h.sum(0))
+        x = self.mixer_norm.add_forward(h, pending)
+        a = self.mixer.forward(x, ctx, view, writes_cache)
+        if probe:
+            probe("attn_norm", x), probe("attn_output", _summed(a))
+        pending = self.mixer_norm.owed(a, S)
+        if self.ff_norm is None:
+            return pending
+        x = self.ff_norm.add_forward(h, pending)
+        out = self.feed_forward.forward(x, ctx)
+        if probe:
+            probe("attn_post_norm", x)
+            if out is not None:
+                probe("ffn_out", _summed(out))
+        return self.ff_norm.owed(out, S)
+
+
+def _with_mult(norm_spec, mult: float):
+    """The norm's description with the factor on its sublayer's result."""
+    from ..config.spec import PartSpec
+    return PartSpec(norm_spec.kind, dict(norm_spec.params, residual_mult=mult), norm_spec.tensors)

@@ -1,6 +1,8 @@
 """Gated feed-forward: down(act(gate x) * (up x)), act = SiLU x/(1+exp(-x))
 (crates/model/src/qwen35/cpu.rs:386-395, crates/model/src/ops.rs:176-178).
-Gate and up are one matrix product over the rows [gate; up]."""
+Gate and up are one matrix product over the rows [gate; up].  ``activation``
+may also be "relu", or ("clamped_swish", slope, limit, shift):
+min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, -limit, limit) + shift)."""
 
 from __future__ import annotations
 
@@ -24,8 +26,12 @@ FUSE_MIN_TOKENS = int(os.environ.get("LLMX_FUSE_MIN_TOKENS", "0"))
 @register_feed_forward("gated_mlp")
 class GatedMLP:
     def __init__(self, spec, weights: dict, rt):
-        if spec.get("activation", "silu") != "silu":
-            raise Unsupported(f"gated_mlp activation {spec.get('activation')!r}: only 'silu' is built")
+        self.activation = spec.get("activation", "silu")
+        if isinstance(self.activation, list):
+            self.activation = tuple(self.activation)
+        name = self.activation if isinstance(self.activation, str) else self.activation[0]
+        if name not in kernels.GATE_ACTS:
+            raise Unsupported(f"gated_mlp activation {name!r}: built are {sorted(kernels.GATE_ACTS)}")
         self.rt, self.F = rt, spec["intermediate_size"]
         t = spec.tensors
         wg, wu = weights.pop(t["gate"].name), weights.pop(t["up"].name)
@@ -52,7 +58,7 @@ class GatedMLP:
     @property
     def takes_row_scales(self) -> bool:
         """The gate|up product can apply a norm's row scales in its epilogue, ahead of the activation."""
-        return self.gate_up._tc is not None
+        return self.gate_up._tc is not None and kernels.gemm_tc_gated_supports(self.activation)
 
     adds_to_residual = True      # forward() takes ``residual`` and may return None: "already added"
 
@@ -61,14 +67,14 @@ class GatedMLP:
         scaled = isinstance(x, RowScaled)
         n_tokens = x.shape[0]
         if tc is not None and x.dtype == torch.bfloat16 and n_tokens > FUSE_MIN_TOKENS and (
-                scaled or kernels.gemm_tc_supports(x, tc.weight)):
+                scaled or kernels.gemm_tc_supports(x, tc.weight)) and kernels.gemm_tc_gated_supports(self.activation):
             # the activation is the epilogue of the gate/up product
-            act = tc.gated(x, self.rt.act_dtype, self.block)
+            act = tc.gated(x, self.rt.act_dtype, self.block, self.activation)
         else:
             assert not scaled
             gu = self.gate_up(x, splits_ok=True)
             act = torch.empty((n_tokens, self.F), dtype=self.rt.act_dtype, device=x.device)
-            kernels.silu_gate(gu, act, self.block)
+            kernels.silu_gate(gu, act, self.block, self.activation)
         if residual is not None and self.down.add_into(act, residual):
             return None
         return self.down(act, splits_ok=True)

@@ -110,13 +110,14 @@ class TensorCoreLinear:
             return x.x, (x.sumsq, x.n_parts, x.eps, x.d)
         return x, None
 
-    def gated(self, x, out_dtype, block: int = 0):
-        """silu(gate x) * (up x), [T, N/2]; ``block`` = 0 for weight = [gate rows; up rows], 16 for
-        blocks of 16 gate rows each followed by the 16 up rows of the same features."""
+    def gated(self, x, out_dtype, block: int = 0, activation="silu"):
+        """act(gate x) * (up x), [T, N/2] (SiLU unless ``activation`` says otherwise, ``kernels.gate_act_args``);
+        ``block`` = 0 for weight = [gate rows; up rows], 16 for blocks of 16 gate rows each followed by the 16 up
+        rows of the same features."""
         x, scale = self._unpack(x)
         out = scratch((x.shape[0], self.N // 2), out_dtype, x.device, "output of the gated matrix product")
         kernels.gemm_tc(x, self.weight, out, gated=2 if block == 16 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS,
-                        scale=scale)
+                        scale=scale, activation=activation)
         return out
 
 def plan_for(weight: torch.Tensor, n_sm: int = 148):

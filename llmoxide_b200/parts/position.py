@@ -5,9 +5,17 @@ and only sin/cos are rounded to float32, as the reference computes it
 (crates/model/src/ops.rs:142-159, base held as float32).  With
 ``angles="float32"`` the angle itself is a float32 product of the position and
 the float32 frequency base^(-2i/n_rot), for designs that compute positions and
-angles in 32-bit.  ``none`` rotates nothing."""
+angles in 32-bit.  With ``scaling`` (factor, original, fast, slow,
+amplitude_slope) the frequencies are stretched for contexts beyond the
+``original`` length: pair i has ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+with lo = max(floor(t(fast)), 0), hi = min(ceil(t(slow)), n_rot - 1) and
+t(turns) = n_rot ln(original / (2 pi turns)) / (2 ln base); its frequency becomes
+f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by
+amplitude_slope * ln(factor) + 1.  ``none`` rotates nothing."""
 
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -21,6 +29,7 @@ class RotaryNeox:
         self.n_rot, self.base, self.rt = int(spec["n_rot"]), float(spec["base"]), rt
         self.factors = spec.get("factors")  # optional per-pair divisors of the angle
         self.angles = spec.get("angles", "float64")
+        self.scaling = spec.get("scaling")
         if self.n_rot % 2:
             raise ValueError(f"n_rot {self.n_rot} must be even")
         self._tables = None
@@ -33,12 +42,13 @@ class RotaryNeox:
             theta = np.arange(n, dtype=np.float64)
             cos = np.empty((n, half), dtype=np.float32)
             sin = np.empty((n, half), dtype=np.float32)
+            freqs, amplitude = self._scaling()
             for i in range(half):
                 if self.angles == "float32":
-                    freq = np.float32(self.base ** (-2.0 * i / self.n_rot))
+                    freq = np.float32(freqs[i])
                     angle = (np.arange(n, dtype=np.float32) * freq).astype(np.float64)
-                    cos[:, i] = np.cos(angle).astype(np.float32)
-                    sin[:, i] = np.sin(angle).astype(np.float32)
+                    cos[:, i] = (np.cos(angle) * amplitude).astype(np.float32)
+                    sin[:, i] = (np.sin(angle) * amplitude).astype(np.float32)
                     continue
                 angle = theta if self.factors is None else theta / float(np.float32(self.factors[i]))
                 cos[:, i] = np.cos(angle).astype(np.float32)
@@ -47,6 +57,26 @@ class RotaryNeox:
             dev = self.rt.device
             self._tables = (torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev), self.n_rot)
         return self._tables
+
+
+    def _scaling(self):
+        """Per pair its frequency, and the factor on cos and sin (1 without ``scaling``)."""
+        half = self.n_rot // 2
+        sc = self.scaling
+        plain = [self.base ** (-2.0 * i / self.n_rot) for i in range(half)]
+        if not sc:
+            return plain, 1.0
+        if self.angles != "float32" or self.factors is not None:
+            raise ValueError("scaled frequencies are built for angles='float32' without per-pair factors")
+        factor, original = float(sc["factor"]), float(sc["original"])
+        turn = lambda turns: self.n_rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+        lo = max(math.floor(turn(float(sc["fast"]))), 0)
+        hi = min(math.ceil(turn(float(sc["slow"]))), self.n_rot - 1)
+        freqs = []
+        for i in range(half):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            freqs.append(plain[i] / factor * ramp + plain[i] * (1.0 - ramp))
+        return freqs, float(sc.get("amplitude_slope", 0.1)) * math.log(factor) + 1.0
 
 
 @register_position("none")

@@ -88,7 +88,12 @@ def host_values(stream: int, lo: int, n: int, mean: float, std: float) -> np.nda
     return np.float32(mean) + np.float32(std) * x
 
 
-def _moments(role: str):
+def _moments(role, init=None):
+    """(mean, standard deviation): the tensor's own (``TensorSpec.init``) or its role's."""
+    if not isinstance(role, str):           # a TensorSpec
+        role, init = role.role, role.init
+    if init is not None:
+        return float(init[0]), float(init[1])
     return (1.0, GAIN_STD) if role == "vector" else (0.0, MATRIX_STD)
 
 
@@ -102,7 +107,7 @@ def _storage_dtype(spec: ModelSpec, role: str, dtype=None) -> torch.dtype:
 def host_tensor(t, seed: int, dtype: torch.dtype) -> torch.Tensor:
     """One tensor of the description on the host, in ``dtype``."""
     stream = _stream_seed(seed, t.name)
-    mean, std = _moments(t.role)
+    mean, std = _moments(t)
     n = int(np.prod(t.shape, dtype=np.int64))
     out = torch.empty(n, dtype=dtype)
 
@@ -156,7 +161,7 @@ def random_tensors_on_device(spec: ModelSpec, seed: int, dtype: str = "bfloat16"
         if not stored.is_floating_point:
             raise ValueError(f"{t.name}: integer tables have no random-weights rule")
         x = torch.empty(t.shape, dtype=target_dtype(stored, dtype), device=device)
-        mean, std = _moments(t.role)
+        mean, std = _moments(t)
         kernels.fill_normal(x, _stream_seed(seed, t.name), q, mean, std, stored)
         out[t.name] = x
     return out
