@@ -74,6 +74,8 @@ class RMSNorm:
 
     def add(self, h, delta) -> None:
         """h += delta (``delta`` [T,d] or split partials [S,T,d], added in order); nothing is normed."""
+        if h.dim() == 2 and isinstance(delta, StreamUpdate):
+            h = h.unsqueeze(0)       # one copy, with connection weights of its own
         if h.dim() == 3:
             if delta is not None:
                 self._streams(h, delta, None, None, True)
@@ -83,6 +85,8 @@ class RMSNorm:
     def add_forward(self, h, delta, rows=None, write_h=True, out_dtype=None, row_scales_ok=False):
         """With ``row_scales_ok`` the caller's next products apply the norm's scale themselves; for a step of
         few tokens the result is then ``RowScaled`` (the norm in two halves, see ``parts.row_scaled``)."""
+        if h.dim() == 2 and isinstance(delta, StreamUpdate):
+            h = h.unsqueeze(0)       # one copy, with connection weights of its own
         if h.dim() == 3:
             n = h.shape[1] if rows is None else rows.numel()
             out = torch.empty((n, self.size), dtype=out_dtype or self.rt.act_dtype, device=h.device)
