@@ -120,7 +120,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_past,
                         float* __restrict__ ws, unsigned int* __restrict__ counters, bf16* __restrict__ out, int H,
-                        int G, int window, int keep_first, float scale_log2, int n_chunks, int cluster_merge) {
+                        int G, int window, int keep_first, float scale_log2, float sink, int n_chunks,
+                        int cluster_merge) {
   using S = DecSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr uint32_t TILE_BYTES = 2u * DEC_TILE * D * 2u;        // what one stage's copies bring
@@ -371,6 +372,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       ls += f * mml[(w * DEC_ROWS + h) * 2 + 1];
     }
     if (n_chunks == 1) {                                                              // nothing to merge with
+      if (sink > 0.f) ls += sink * exp2f(-mx);       // the sink: keys of score 0 without a value (mx in log2 units)
       __nv_bfloat162 lo = __floats2bfloat162_rn(a.x / ls, a.y / ls), hi = __floats2bfloat162_rn(a.z / ls, a.w / ls);
       *reinterpret_cast<uint2*>(out + ((size_t)b * H + h0 + h) * D + d) =
           make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
@@ -435,6 +437,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
           l += w * lc[c];
         }
       }
+      if (sink > 0.f) l += sink * exp2f(-mx);        // the sink joins the merged denominator once
       const float r = 1.f / l;
       __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * r, a.y * r), hi2 = __floats2bfloat162_rn(a.z * r, a.w * r);
       uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi2));
@@ -481,6 +484,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       f[c] = w;
       if (w != 0.f) l += w * ls[c];
     }
+    if (sink > 0.f) l += sink * exp2f(-mx);          // the sink joins the merged denominator once
     inv[threadIdx.x] = 1.f / l;
   }
   __syncthreads();
@@ -510,7 +514,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 template <int D>
 static int launch_decode(const void* q, void* out, const void* k_cache, const void* v_cache, long long n_pages,
                          const int* block_table, int table_width, const int* seq_past, float* ws, unsigned int* counters, int B, int H, int G,
-                         int window, int keep_first, float scale, int n_chunks, cudaStream_t stream) {
+                         int window, int keep_first, float scale, float sink, int n_chunks, cudaStream_t stream) {
   const int R = H / G;
   const int head_groups = (R + DEC_ROWS - 1) / DEC_ROWS;
   dim3 grid(n_chunks, G * head_groups, B);
@@ -538,11 +542,11 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
   if (cluster_merge)
     launch_pdl_cluster(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, (unsigned)n_chunks, mk, mv, (const bf16*)q,
                        (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters,
-                       (bf16*)out, H, G, window, keep_first, scale * 1.4426950408889634f, n_chunks, cluster_merge);
+                       (bf16*)out, H, G, window, keep_first, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge);
   else
     launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, mk, mv, (const bf16*)q, (const bf16*)k_cache,
                (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters, (bf16*)out, H, G, window,
-               keep_first, scale * 1.4426950408889634f, n_chunks, cluster_merge);
+               keep_first, scale * 1.4426950408889634f, sink, n_chunks, cluster_merge);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -552,11 +556,13 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
 // of B*H*n_chunks*(D+4) elements (16-byte aligned), and counters holds B * G * ceil((H/G)/8) words that are zero before the first
 // launch (each launch leaves them zero).
 // keep_first: under a window, the sequence's first keep_first keys stay visible.
-LLMX_API int llmx_attention_decode_keep(const void* q, void* out, const void* k_cache, const void* v_cache,
+// sink: added to the softmax's denominator (as many keys of score 0 that have no value); 0 for none.
+LLMX_API int llmx_attention_decode_sink(const void* q, void* out, const void* k_cache, const void* v_cache,
                                         long long n_pages, const int* block_table, int table_width, const int* seq_past,
                                         float* ws, unsigned int* counters, int B, int H, int G, int D, int window,
-                                        int keep_first, float scale, int n_chunks, cudaStream_t stream) {
+                                        int keep_first, float scale, float sink, int n_chunks, cudaStream_t stream) {
   if (B <= 0) return 0;
+  if (!(sink >= 0.f)) return LLMX_REFUSED(1);
   if (window <= 0) keep_first = 0;
   if (H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || n_chunks < 1 || n_chunks > DEC_MAX_CHUNKS ||
       (n_chunks > 8 && (!ws || !counters || ((uintptr_t)ws & 15))) || n_pages <= 0 ||
@@ -566,13 +572,21 @@ LLMX_API int llmx_attention_decode_keep(const void* q, void* out, const void* k_
 #define CASE(DD)                                                                                               \
   case DD:                                                                                                     \
     return launch_decode<DD>(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, \
-                             B, H, G, window, keep_first, scale, n_chunks, stream)
+                             B, H, G, window, keep_first, scale, sink, n_chunks, stream)
   switch (D) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
     CASE(144); CASE(160); CASE(176); CASE(192); CASE(208); CASE(224); CASE(240); CASE(256);
     default: return LLMX_REFUSED(1);
   }
 #undef CASE
+}
+
+LLMX_API int llmx_attention_decode_keep(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                        long long n_pages, const int* block_table, int table_width, const int* seq_past,
+                                        float* ws, unsigned int* counters, int B, int H, int G, int D, int window,
+                                        int keep_first, float scale, int n_chunks, cudaStream_t stream) {
+  return llmx_attention_decode_sink(q, out, k_cache, v_cache, n_pages, block_table, table_width, seq_past, ws, counters, B,
+                                    H, G, D, window, keep_first, scale, 0.f, n_chunks, stream);
 }
 
 // 0; 1 after a launch in which a copy into shared memory never completed, 2 after one whose shared memory was

@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ k_cache,
                          const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_past, int H, int G,
-                         int window, int keep_first, float scale_log2) {
+                         int window, int keep_first, float scale_log2, float sink) {
   constexpr int CHUNKS = D / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;             // k-steps of the score product
   constexpr int TILE_BYTES = PF_BK * D * 2;
@@ -235,6 +235,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  // a sink: `sink` keys of score 0 without a value; they only add to the denominator (m is in log2 units)
+  if (sink > 0.f) {
+    l0 += sink * exp2f(-m0);
+    l1 += sink * exp2f(-m1);
+  }
   const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
   const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
 #pragma unroll
@@ -252,7 +257,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
 template <int D>
 static int launch_prefill(const void* q, void* out, const void* k_cache, const void* v_cache, const int* block_table,
                           int table_width, const int* seq_start, const int* seq_past, int B, int max_new, int H,
-                          int G, int window, int keep_first, float scale, cudaStream_t stream) {
+                          int G, int window, int keep_first, float scale, float sink, cudaStream_t stream) {
   const size_t smem = (size_t)PF_BQ * D * 2 + 4 * (size_t)PF_BK * D * 2;
   auto kernel = attention_prefill_kernel<D>;
   static bool attr_set = false;
@@ -264,7 +269,7 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
   dim3 grid(H, (max_new + PF_BQ - 1) / PF_BQ, B);
   launch_pdl(kernel, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                              block_table, table_width, seq_start, seq_past, H, G, window,
-                                             keep_first, scale * 1.4426950408889634f);
+                                             keep_first, scale * 1.4426950408889634f, sink);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -274,16 +279,16 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
 LLMX_API int llmx_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,
                                     const int* block_table, int table_width, const int* seq_start,
                                     const int* seq_past, int B, int max_new, int H, int G, int D, int window,
-                                    int keep_first, float scale, cudaStream_t stream) {
+                                    int keep_first, float scale, float sink, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 ||
       (max_new + PF_BQ - 1) / PF_BQ > 65535)
     return LLMX_REFUSED(1);
   if (D == 128)
     return launch_prefill<128>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new,
-                               H, G, window, window > 0 ? keep_first : 0, scale, stream);
+                               H, G, window, window > 0 ? keep_first : 0, scale, sink, stream);
   if (D == 64)
     return launch_prefill<64>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new, H,
-                              G, window, window > 0 ? keep_first : 0, scale, stream);
+                              G, window, window > 0 ? keep_first : 0, scale, sink, stream);
   return LLMX_REFUSED(1);
 }

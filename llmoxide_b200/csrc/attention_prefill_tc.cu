@@ -60,7 +60,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
                             const int* __restrict__ seq_past, int H, int G, int window, int keep_first,
-                            float scale_log2) {
+                            float scale_log2, float sink) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   pdl_launch_dependents();
   pdl_wait();
@@ -305,7 +305,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     if (ok) {
       tc_fence_after();
-      const float inv = 1.0f / l;
+      // a sink: `sink` keys of score 0 without a value; they only add to the denominator (l is in units of 2^-m_used)
+      const float inv = 1.0f / ((sink > 0.f && row_live) ? l + sink * exp2f(-m_used) : l);
       bf16* orow = out + ((size_t)(tok0 + i0 + row) * H + hq) * AT_D;
 #pragma unroll 1
       for (int c = 0; c < AT_D; c += 32) {
@@ -343,7 +344,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,
                                        long long n_pages, const int* block_table, int table_width,
                                        const int* seq_start, const int* seq_past, int B, int T, int max_new, int H,
-                                       int G, int D, int window, int keep_first, float scale, cudaStream_t stream) {
+                                       int G, int D, int window, int keep_first, float scale, float sink,
+                                       cudaStream_t stream) {
   if (B <= 0 || max_new <= 0 || T <= 0) return 0;
   if (window <= 0) keep_first = 0;
   if (D != AT_D || H <= 0 || G <= 0 || H % G || window < 0 || keep_first < 0 || B > 65535 || (max_new + AT_ROWS - 1) / AT_ROWS > 65535 || n_pages <= 0)
@@ -368,7 +370,7 @@ LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_c
   }
   dim3 grid(H, (max_new + AT_ROWS - 1) / AT_ROWS, B);
   launch_pdl(attention_prefill_tc_kernel, grid, dim3(AT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, block_table,
-             table_width, seq_start, seq_past, H, G, window, keep_first, scale * 1.4426950408889634f);
+             table_width, seq_start, seq_past, H, G, window, keep_first, scale * 1.4426950408889634f, sink);
   return LLMX_LAUNCH_STATUS();
 }
 

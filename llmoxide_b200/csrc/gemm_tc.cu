@@ -69,7 +69,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(int n) {
 template <int BN, int MODE, typename TY>
 __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, bool store, TY* __restrict__ out,
                                               int n0, int t0, int T, int n_limit, long long ldy, int quad, int lane,
-                                              const float* row_scale = nullptr) {
+                                              const GateAct act, const float* row_scale = nullptr) {
   const int row = quad * 32 + lane;
   const int n = MODE == 2 ? (n0 >> 1) + quad * 16 + (lane & 15) : n0 + row;
   const bool upper = lane >= 16;
@@ -100,7 +100,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, 
         const float up = upper ? v[e + 1] : got;
         const int t = t0 + c + e + (upper ? 1 : 0);
         if (store && n < n_limit && t < T)
-          out[(size_t)t * ldy + n] = from_f32<TY>(__fdividef(gate, 1.0f + __expf(-gate)) * up);
+          out[(size_t)t * ldy + n] = from_f32<TY>(gated_act_fast(act, gate, up));
       }
     } else if (store && n < n_limit) {
 #pragma unroll
@@ -108,7 +108,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, 
         const int t = t0 + c + e;
         if (t < T) {
           float r = v[e];
-          if (MODE != 0) r = __fdividef(r, 1.0f + __expf(-r)) * g[e];
+          if (MODE != 0) r = gated_act_fast(act, r, g[e]);
           out[(size_t)t * ldy + n] = from_f32<TY>(r);
         }
       }
@@ -130,7 +130,7 @@ struct TcStage {
 template <int BN, int MODE, typename TY>
 __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CUtensorMap* map_y, TY* stage,
                                                      int& chunk_no, int n0, int t0, int split, int T, int quad,
-                                                     int lane, bool first_thread, bool accumulate) {
+                                                     int lane, bool first_thread, bool accumulate, const GateAct act) {
   static_assert(MODE != 1, "one accumulator");
   constexpr int ROWS = TcStage<TY>::ROWS;
   constexpr int COLS = MODE == 2 ? 64 : 128;
@@ -151,7 +151,7 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CU
         const float got = __shfl_xor_sync(0xffffffffu, upper ? v[e] : v[e + 1], 16);
         const float gate = upper ? got : v[e];
         const float up = upper ? v[e + 1] : got;
-        buf[(e + (upper ? 1 : 0)) * COLS + col] = from_f32<TY>(__fdividef(gate, 1.0f + __expf(-gate)) * up);
+        buf[(e + (upper ? 1 : 0)) * COLS + col] = from_f32<TY>(gated_act_fast(act, gate, up));
       }
     } else {
 #pragma unroll
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TY* __restrict__ Y, int T, int N, int K, long long ldy, int k_blocks_per_split,
                long long split_stride, int F, int n_stages, int row_tiles, int token_tiles, int n_units,
-               const TcScale sc) {
+               const TcScale sc, const GateAct act) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;   // MODE 2 has one accumulator: gate and up rows share a tile
   constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -361,7 +361,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       TY* out = Y + (MODE == 0 ? (size_t)split * split_stride : 0);
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<BN, MODE, TY>(acc_addr, n_kb > 0, true, out, n0, t0, T, n_limit, ldy, quad, lane, row_scale);
+      epilogue_tile<BN, MODE, TY>(acc_addr, n_kb > 0, true, out, n0, t0, T, n_limit, ldy, quad, lane, act, row_scale);
       // hand the accumulator set back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -478,7 +478,7 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_y, TY* __restrict__ Y, int T, int N, int K, long long ldy,
                     int F, int n_stages, int row_pairs, int token_tiles, int n_units, int group_tiles, int staged,
-                    int accumulate, int kb_per_split, long long split_stride) {
+                    int accumulate, int kb_per_split, long long split_stride, const GateAct act) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr int HALF = BN / 2;                                              // tokens this CTA loads
@@ -650,10 +650,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
       if (MODE != 1 && staged)
         epilogue_tile_staged<BN, MODE == 1 ? 0 : MODE, TY>(acc_addr, &map_y, stage_buf, chunk_no, n0, t0, split, T, quad,
-                                                             lane, threadIdx.x == 64, accumulate != 0);
+                                                             lane, threadIdx.x == 64, accumulate != 0, act);
       else
         epilogue_tile<BN, MODE, TY>(acc_addr, true, true, Y + (size_t)split * split_stride, n0, t0, T, n_limit, ldy, quad,
-                                    lane);
+                                    lane, act);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_remote_arrive(leader_acc_empty0 + 8u * buf);
@@ -679,6 +679,16 @@ static int sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
   }
   return n;
+}
+
+// The gated activation of the launches that follow from this thread (modes 1 and 2): it travels to the kernel as
+// an argument, so a launch, or a captured graph node, keeps the one that was set when it was made.  SiLU until
+// set otherwise; kinds in common.cuh.
+static thread_local GateAct t_gate_act = {LLMX_ACT_SILU, 1.f, 0.f, 0.f};
+LLMX_API int llmx_gemm_tc_gate_act(int kind, float slope, float limit, float shift) {
+  if (kind < LLMX_ACT_SILU || kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  t_gate_act = GateAct{kind, slope, limit, shift};
+  return 0;
 }
 
 template <int BN, int MODE, typename TY>
@@ -716,7 +726,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   const int max_ctas = sm_count() * ctas_per_sm;
   const int grid = n_units < max_ctas ? (int)n_units : max_ctas;
   launch_pdl(kernel, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, (TY*)Y, T, N, K, ldy, per_split,
-             split_stride, F, stages, row_tiles, token_tiles, (int)n_units, sc);
+             split_stride, F, stages, row_tiles, token_tiles, (int)n_units, sc, t_gate_act);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -854,7 +864,8 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   cfg.gridDim = dim3(2 * pairs);
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, my, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
-                                     (int)n_units, (int)group_tiles, staged, accumulate, kb_per_split, split_stride);
+                                     (int)n_units, (int)group_tiles, staged, accumulate, kb_per_split, split_stride,
+                                     t_gate_act);
   if (e != cudaSuccess) return (int)e;
   return LLMX_LAUNCH_STATUS();
 }

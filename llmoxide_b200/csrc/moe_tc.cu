@@ -11,7 +11,7 @@
 // fit, so a unit's epilogue overlaps the next unit's MMAs.  Roles per CTA: one thread issues the copies, one the
 // MMAs, four warps read the accumulators back (tcgen05.ld) and finish the unit:
 //
-//   MODE 1 (gate|up): two accumulators, rows n and n + F of the expert's [2F, K]; act[row, n] = silu(gate) * up
+//   MODE 1 (gate|up): two accumulators, rows n and n + F of the expert's [2F, K]; act[row, n] = gated_act(gate, up) (common.cuh)
 //   MODE 0 (down):    y[dest[row]][n] = weight[row] * acc, float32 (dest = choice * tokens + token, from the sort)
 //
 // Which expert a unit reads is decided on the device by the kernel before, so every thread waits for that
@@ -34,7 +34,8 @@ template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(MT_THREADS)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       TY* __restrict__ Y, const int* __restrict__ tiles, int max_tiles, const int* __restrict__ dest,
-                      const float* __restrict__ sorted_weight, int N, int K, int w_rows, int n_stages, int row_tiles) {
+                      const float* __restrict__ sorted_weight, int N, int K, int w_rows, int n_stages, int row_tiles,
+                      const GateAct act) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr uint32_t A_BYTES = MT_BM * MT_BK * 2;
@@ -194,8 +195,7 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const int r = c + i;
             if (r >= n_rows) break;
             if (MODE == 1) {
-              const float a = v[i];
-              Y[(size_t)(row0 + r) * N + n] = from_f32<TY>(__fdividef(a, 1.0f + __expf(-a)) * g[i]);
+              Y[(size_t)(row0 + r) * N + n] = from_f32<TY>(gated_act_fast(act, v[i], g[i]));
             } else {
               Y[(size_t)tile_dest[r] * N + n] = from_f32<TY>(tile_weight[r] * v[i]);
             }
@@ -227,7 +227,7 @@ static int mt_sm_count() {
 
 template <int BN, int MODE, typename TY>
 static int mt_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, const int* tiles, int max_tiles, const int* dest,
-                     const float* sorted_weight, int N, int K, int w_rows, cudaStream_t stream) {
+                     const float* sorted_weight, int N, int K, int w_rows, const GateAct act, cudaStream_t stream) {
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr size_t STAGE = (size_t)N_ACC * MT_BM * MT_BK * 2 + (size_t)BN * MT_BK * 2;
   const int row_tiles = (N + MT_BM - 1) / MT_BM;
@@ -250,7 +250,7 @@ static int mt_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, cons
   const int max_ctas = mt_sm_count() * ctas_per_sm;
   const int grid = n_units < max_ctas ? (int)n_units : max_ctas;
   launch_pdl(kernel, dim3(grid), dim3(MT_THREADS), smem, stream, mw, mx, (TY*)Y, tiles, max_tiles, dest, sorted_weight, N, K,
-             w_rows, stages, row_tiles);
+             w_rows, stages, row_tiles, act);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -260,8 +260,11 @@ static int mt_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, cons
 // (dest and sorted_weight [P] in sorted order, from the sort).
 LLMX_API int llmx_moe_grouped_tc(const void* X, long long ldx, long long P, const void* W, int n_experts, void* Y,
                                  const int* tiles, int max_tiles, int tile_rows, const int* dest,
-                                 const float* sorted_weight, int N, int K, int gated, cudaStream_t stream) {
+                                 const float* sorted_weight, int N, int K, int gated, int act_kind, float slope, float limit,
+                                 float shift, cudaStream_t stream) {
   if (P <= 0) return 0;
+  if (act_kind < LLMX_ACT_SILU || act_kind > LLMX_ACT_CLAMPED_SWISH) return LLMX_REFUSED(1);
+  const GateAct act = {act_kind, slope, limit, shift};
   if (N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || max_tiles <= 0 ||
       n_experts <= 0 || (!gated && (!dest || !sorted_weight)))
     return LLMX_REFUSED(1);
@@ -270,8 +273,8 @@ LLMX_API int llmx_moe_grouped_tc(const void* X, long long ldx, long long P, cons
   if (make_map(&mw, W, (uint64_t)n_experts * w_rows, (uint64_t)K, (uint64_t)K, MT_BM, true)) return LLMX_REFUSED(4);
   if (make_map(&mx, X, (uint64_t)P, (uint64_t)K, (uint64_t)ldx, (uint32_t)tile_rows, false)) return LLMX_REFUSED(4);
 #define GO(BN)                                                                                                      \
-  return gated ? mt_launch<BN, 1, bf16>(mw, mx, Y, tiles, max_tiles, dest, sorted_weight, N, K, w_rows, stream) \
-               : mt_launch<BN, 0, float>(mw, mx, Y, tiles, max_tiles, dest, sorted_weight, N, K, w_rows, stream)
+  return gated ? mt_launch<BN, 1, bf16>(mw, mx, Y, tiles, max_tiles, dest, sorted_weight, N, K, w_rows, act, stream) \
+               : mt_launch<BN, 0, float>(mw, mx, Y, tiles, max_tiles, dest, sorted_weight, N, K, w_rows, act, stream)
   switch (tile_rows) {
     case 16: GO(16);
     case 64: GO(64);

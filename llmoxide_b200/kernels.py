@@ -518,7 +518,8 @@ def _counters(device, n: int):
 
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
-                     head_dim: int, window, scale: float, n_chunks: int = 0, keep_first: int = 0) -> None:
+                     head_dim: int, window, scale: float, n_chunks: int = 0, keep_first: int = 0,
+                     sink: float = 0.0) -> None:
     """One new token per sequence, bfloat16: q, out [B,H*D] in batch order;
     seq_past[b] is the token's position.  Each sequence's keys are split over
     n_chunks CTAs (0: chosen from the batch's shape), which merge inside a
@@ -539,13 +540,13 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
         ws = guard.scratch((B * n_heads * n_chunks * (head_dim + 4),), torch.float32, q.device,
                            "decode attention workspace")
         counters = _counters(q.device, B * n_kv_heads * ((group + 7) // 8))
-    f = _fn("attention_decode", "llmx_attention_decode_keep",
+    f = _fn("attention_decode", "llmx_attention_decode_sink",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1],
              _ptr(seq_past), _ptr(ws), _ptr(counters), B, n_heads, n_kv_heads, head_dim, int(window or 0),
-             int(keep_first or 0), scale, n_chunks, _stream()), "attention_decode")
+             int(keep_first or 0), scale, float(sink or 0.0), n_chunks, _stream()), "attention_decode")
 
 
 def attention_decode_status() -> int:
@@ -560,7 +561,8 @@ def attention_prefill_supports(q, k_cache, head_dim: int) -> bool:
 
 
 def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
-                      n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0) -> None:
+                      n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0,
+                      sink: float = 0.0) -> None:
     """Prompt attention on the tensor cores, bfloat16, head sizes 64 and 128:
     q, out [T,H*D] packed sequence after sequence.  Under a window the first ``keep_first`` keys stay visible."""
     _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
@@ -569,14 +571,15 @@ def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past
         raise Unsupported(f"the tiled prompt attention takes bfloat16 and head sizes 64 or 128, not {head_dim}")
     f = _fn("attention_prefill", "llmx_attention_prefill",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(seq_start), _ptr(seq_past), n_seqs, max_new, n_heads, n_kv_heads, head_dim, int(window or 0),
-             int(keep_first or 0), scale, _stream()), "attention_prefill")
+             int(keep_first or 0), scale, float(sink or 0.0), _stream()), "attention_prefill")
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
-                         n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0) -> None:
+                         n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float, keep_first: int = 0,
+                         sink: float = 0.0) -> None:
     """Prompt attention on tcgen05, bfloat16, head size 128: q, out [T,H*128]
     packed sequence after sequence; the cache entry is [n_pages,G,64,128]."""
     _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
@@ -586,10 +589,11 @@ def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_p
         raise Unsupported("the tcgen05 prompt attention takes bfloat16 and head size 128")
     f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
              block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, q.shape[0], max_new, n_heads,
-             n_kv_heads, head_dim, int(window or 0), int(keep_first or 0), scale, _stream()), "attention_prefill_tc")
+             n_kv_heads, head_dim, int(window or 0), int(keep_first or 0), scale, float(sink or 0.0), _stream()),
+           "attention_prefill_tc")
 
 
 def attention_prefill_tc_status(reset: bool = True) -> int:
@@ -626,7 +630,21 @@ def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_tc_gated_supports(activation) -> bool:
     """Whether the tensor-core product applies this gated activation in its epilogue."""
-    return activation == "silu"
+    return (activation if isinstance(activation, str) else activation[0]) in GATE_ACTS
+
+
+_tc_gate_act = [("silu",)]        # what the gemm_tc library was last told
+
+
+def _set_tc_gate_act(activation) -> None:
+    """The gated activation of the tensor-core launches that follow (a kernel argument, set on the host)."""
+    key = gate_act_args(activation)
+    if _tc_gate_act[0] != key:
+        f = _fn("gemm_tc", "llmx_gemm_tc_gate_act", [c_int, c_float, c_float, c_float])
+        code = f(*key)
+        if code:
+            raise Unsupported(f"gemm_tc: activation {activation!r} refused")
+        _tc_gate_act[0] = key
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1, gated=False,
@@ -647,8 +665,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
     T, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.is_contiguous()
-    if gated and not gemm_tc_gated_supports(activation):
-        raise Unsupported(f"the tensor-core product has no epilogue for the activation {activation!r}")
+    if gated:
+        if not gemm_tc_gated_supports(activation):
+            raise Unsupported(f"the tensor-core product has no epilogue for the activation {activation!r}")
+        _set_tc_gate_act(activation)
     if gated:
         assert n_split == 1 and out.shape == (T, N // 2)
         ldy, stride = N // 2, 0
@@ -871,7 +891,7 @@ def moe_tc_supports(x, w) -> bool:
 
 def moe_tc_gated_supports(activation) -> bool:
     """Whether the tensor-core grouped product applies this gated activation in its epilogue."""
-    return activation == "silu"
+    return (activation if isinstance(activation, str) else activation[0]) in GATE_ACTS
 
 
 def moe_gather_rows(x, perm, top: int, xs) -> None:
@@ -895,9 +915,9 @@ def moe_grouped_tc(xs, w, y, tiles, tile_rows: int, dest, sorted_weight, gated: 
     assert w.shape[2] == K and y.dtype == (torch.bfloat16 if gated else torch.float32)
     f = _fn("moe_tc", "llmx_moe_grouped_tc",
             [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
     _check(f(_ptr(xs), xs.stride(0), xs.shape[0], _ptr(w), w.shape[0], _ptr(y), _ptr(tiles), tiles.shape[0], tile_rows,
-             _ptr(dest), _ptr(sorted_weight), N, K, int(gated), _stream()), "moe_grouped_tc")
+             _ptr(dest), _ptr(sorted_weight), N, K, int(gated), *gate_act_args(activation), _stream()), "moe_grouped_tc")
 
 
 def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gated: bool, activation="silu") -> None:

@@ -111,7 +111,7 @@ class GQAttention:
         libs = {"elementwise"} | self.q_only.libraries() | self.o.libraries()
         if self.staged:
             libs.add("short_conv")
-        if not self.plain or self.sink:
+        if not self.plain:
             return libs | {"attention"}
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
             libs |= {"attention_decode",
@@ -173,18 +173,18 @@ class GQAttention:
         a window that keeps its first keys."""
         H, G, D = self.H, self.G, self.D
         fast = (self.plain and q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16
-                and self.rt.tensor_cores and not self.sink)
+                and self.rt.tensor_cores and self.scale > 0)       # (the tiled kernels take the maximum before the scale)
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
-                                     self.scale, keep_first=self.keep_first)
+                                     self.scale, keep_first=self.keep_first, sink=self.sink)
         elif fast and D == 128:
             kernels.attention_prefill_tc(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                          ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
-                                         keep_first=self.keep_first)
+                                         keep_first=self.keep_first, sink=self.sink)
         elif fast and kernels.attention_prefill_supports(q, view.k, D):
             kernels.attention_prefill(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                       ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale,
-                                      keep_first=self.keep_first)
+                                      keep_first=self.keep_first, sink=self.sink)
         else:
             kernels.attention_paged(q, out, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                     H, G, D, self.window, self.scale, v_head_dim=self.Dv, keep_first=self.keep_first,

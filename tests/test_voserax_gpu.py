@@ -266,6 +266,98 @@ def test_one_key_stands_out_at_every_edge_of_the_window_with_a_sink(D, Dv, H, G,
     assert torch.allclose(out.cpu(), torch.full((1, H * Dv), 0.5))
 
 
+def _paged_case(lens, G, D, seed):
+    """A cache of random keys and values for sequences of the given lengths, pages dealt out in any order."""
+    from llmoxide_b200 import kernels
+
+    g = torch.Generator().manual_seed(seed)
+    page = kernels.PAGE
+    per = [(n + page - 1) // page for n in lens]
+    order = torch.randperm(sum(per) + 2, generator=g).tolist()
+    table = torch.full((len(lens), max(per)), -1, dtype=torch.int32)
+    kc = torch.randn((sum(per) + 2, G, page, D), generator=g) * 0.3
+    vc = torch.randn((sum(per) + 2, G, page, D), generator=g)
+    at = 0
+    for b, n in enumerate(per):
+        table[b, :n] = torch.tensor(order[at : at + n], dtype=torch.int32)
+        at += n
+    return table, kc.to(torch.bfloat16), vc.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("D, H, G", [(64, 8, 1), (128, 4, 2), (48, 3, 3), (96, 4, 1)])
+@pytest.mark.parametrize("window", [40, 130, 1, 64, 0])
+def test_decode_attention_with_a_sink_equals_the_general_kernel(D, H, G, window):
+    """One token per sequence at lengths around the window's and the pages' edges; the key just outside or just
+    inside the window is made to stand out, so that a mask that is one key off changes the result beyond any
+    tolerance; where no key stands out (short sequences, small scores) the sink holds a large share of the
+    denominator.  Every split of the keys gives the same answer: the sink joins the merged denominator once."""
+    from llmoxide_b200 import kernels
+
+    lens = [n for n in [1, 2, 3, window + 1, window + 2, window + 3, 64, 65, 200, 399, 129, 257] if n >= 1]
+    table, kc, vc = _paged_case(lens, G, D, seed=D + window)
+    B = len(lens)
+    q = (torch.randn(B, H, D, generator=torch.Generator().manual_seed(1)) * 0.3).to(torch.bfloat16)
+    page = kernels.PAGE
+    for b, n in enumerate(lens):
+        p = n - 1
+        spots = [p - window, p - window + 1, None] if window else [0, p, None]
+        j = spots[b % 3]
+        if j is not None and 0 <= j <= p:
+            for g in range(G):
+                kc[table[b, j // page], g, j % page] = (q[b, g * (H // G)].float() * 6.0).to(torch.bfloat16)
+    past = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    qd, kd, vd, td = q.view(B, H * D).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)
+    want = torch.empty((B, H * D), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_paged(qd, want, kd, vd, td, seq, past, H, G, D, window or None, 0.7, sink=1.0)
+    without = torch.empty_like(want)
+    kernels.attention_paged(qd, without, kd, vd, td, seq, past, H, G, D, window or None, 0.7)
+    assert _rel(without.float().cpu().numpy(), want.float().cpu().numpy()) > 0.1       # the sink shows
+    for n_chunks in (0, 1, 3, 8, 11):
+        got = torch.empty_like(want)
+        kernels.attention_decode(qd, got, kd, vd, td, past, H, G, D, window or None, 0.7, n_chunks=n_chunks, sink=1.0)
+        assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2, (n_chunks,)
+    kernels.check_status()
+
+
+@pytest.mark.parametrize("D, H, G", [(64, 8, 1), (128, 4, 2)])
+@pytest.mark.parametrize("window", [40, 130, 1, 64, 0])
+def test_prompt_attention_with_a_sink_equals_the_general_kernel(D, H, G, window):
+    """Whole prompts and later portions (129 and 2 tokens after a cached prefix) in one launch."""
+    from llmoxide_b200 import kernels
+
+    lens = [1, 70, 200, 399, 257, 66]
+    new = [1, 70, 200, 129, 2, 65]              # the last `new` tokens of each are this step's
+    table, kc, vc = _paged_case(lens, G, D, seed=3 * D + window)
+    T = sum(new)
+    q = (torch.randn(T, H, D, generator=torch.Generator().manual_seed(2)) * 0.3).to(torch.bfloat16)
+    start = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    tok_seq = np.concatenate([[b] * n for b, n in enumerate(new)]).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(L - n, L) for L, n in zip(lens, new)]).astype(np.int32)
+    page = kernels.PAGE
+    for b, L in enumerate(lens):                # a key that stands out for the sequence's last query
+        p = L - 1
+        j = [p - window, p - window + 1][b % 2] if window else [0, p][b % 2]
+        if 0 <= j <= p:
+            for g in range(G):
+                kc[table[b, j // page], g, j % page] = (q[start[b + 1] - 1, g * (H // G)].float() * 6.0).to(torch.bfloat16)
+    qd, kd, vd, td = q.view(T, H * D).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)
+    want = torch.empty((T, H * D), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_paged(qd, want, kd, vd, td, torch.tensor(tok_seq, device=DEV), torch.tensor(tok_pos, device=DEV),
+                            H, G, D, window or None, 0.7, sink=1.0)
+    pasts = torch.tensor([L - n for L, n in zip(lens, new)], dtype=torch.int32, device=DEV)
+    got = torch.empty_like(want)
+    kernels.attention_prefill(qd, got, kd, vd, td, torch.tensor(start, device=DEV), pasts, len(lens), max(new), H, G, D,
+                              window or None, 0.7, sink=1.0)
+    assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2
+    if D == 128:            # the tcgen05 kernel of that head size
+        got = torch.empty_like(want)
+        kernels.attention_prefill_tc(qd, got, kd, vd, td, torch.tensor(start, device=DEV), pasts, len(lens), max(new), H, G,
+                                     D, window or None, 0.7, sink=1.0)
+        assert _rel(got.float().cpu().numpy(), want.float().cpu().numpy()) < 1.5e-2
+        kernels.check_status()
+
+
 # ---------------------------------------------------------------------------------------------------------
 # feed-forwards
 # ---------------------------------------------------------------------------------------------------------
