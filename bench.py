@@ -6,6 +6,7 @@ B200.  A "step" is one decode step of a batch of 8 sequences from depth 2048
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
     python bench.py --cpu-baseline      # the plain implementation of tests/ on the CPU, tiny configurations
     python bench.py --design tifapel    # the Tifapel decoder beside the dense decoder at equal layer sizes
+    python bench.py --design voserax    # the Voserax decoder beside the Tifapel decoder's attention layers, two sizes
 
 ``value`` is device-timed (CUDA events around K steps queued back to back);
 ``e2e`` is the same metric through ``Session.generate`` with host token ids in
@@ -194,7 +195,7 @@ def main() -> int:
                          "one replayed decode step, when each kernel's dependency resolved")
     ap.add_argument("--cpu-baseline", action="store_true",
                     help="instead of the benchmark: time the plain implementation of tests/ on the CPU (tiny configurations)")
-    ap.add_argument("--design", choices=["tifapel"], default=None,
+    ap.add_argument("--design", choices=["tifapel", "voserax"], default=None,
                     help="instead of the benchmark: prefill and decode rates of that design at layer sizes of a real "
                          "model (random weights), beside the dense Qwen3 decoder at equal sizes, with every kernel's "
                          "time per step (one JSON line of its own; the default workload is untouched)")
@@ -416,13 +417,31 @@ def tifapel_layers(n_layers, width, heads, kv_heads, dim, window, keep, experts,
     return out
 
 
+def voserax_layers(n_layers, width, heads, kv_heads, dim, window, experts, top, ff, shared_ff):
+    """Attention layers with a 4-tap convolution, rotation over half a head with scaled frequencies, mixed values;
+    the first feed-forward dense, the others routed with two identity experts and a shared expert."""
+    mixer = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, conv=4, mask=dict(size=window),
+                 rot=dict(dims=dim // 2, base=10000.0, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0)),
+                 v_mix=True)
+    moe = dict(kind="moe", expert=dict(ff=ff, limit=7.0), router=dict(experts=experts, top=top, identity=2),
+               shared=dict(ff=shared_ff, limit=7.0))
+    return [dict(type="attention", mixer=json.loads(json.dumps(mixer)),
+                 mlp=dict(kind="dense", ff=top * ff + shared_ff) if i == 0 else json.loads(json.dumps(moe)))
+            for i in range(n_layers)]
+
+
 def design_bench(args) -> int:
-    """Prefill and decode rates of the Tifapel decoder at layer sizes that resemble a real model's (width 2048,
+    """``--design tifapel``: prefill and decode rates of the Tifapel decoder at layer sizes that resemble a real model's (width 2048,
     16 heads of 128 on 4 key/value heads, a window of 1024 that keeps 4 tokens, 16 experts of 1024 of which a
     token uses 2 from 2 of 4 groups), beside the dense Qwen3 decoder with the same width, heads and layer count and
     a feed-forward as wide as a token's two experts.  Device-timed with CUDA events, median of 5; weights and
     cache are larger than L2.  Then one prompt step and one decode step of each model with every kernel between
-    two events of its own (no launch overlaps another), summed by kernel."""
+    two events of its own (no launch overlaps another), summed by kernel.
+
+    ``--design voserax``: the same measurement of the Voserax decoder (four streams, a 4-tap convolution, a sink,
+    mixed values, experts with identity and shared experts) at two sizes (width 2048 with 16 heads of 128 and 16
+    experts of 1024; width 1024 with 16 heads of 64 and 8 experts of 512), beside the closest model of this package at
+    equal sizes: the Tifapel decoder's attention layers with routed experts."""
     import numpy as np
     import torch
 
@@ -430,11 +449,32 @@ def design_bench(args) -> int:
     from llmoxide_b200 import Engine, LoadOptions, kernels, read_config
 
     L = min(args.layers, 8) if args.layers != QWEN3_8B["num_hidden_layers"] else 8
-    width, heads, kv, dim, window, keep, E, top, ff = 2048, 16, 4, 128, 1024, 4, 16, 2, 1024
     vocab = 32768
     T, B, depth = args.prefill_tokens, args.batch, args.depth
     pk, pk_src = peaks()
     rng = np.random.default_rng(0)
+    if args.design == "voserax":
+        runs = []
+        for width, heads, kv, dim, window, E, top, ff in ((2048, 16, 4, 128, 1024, 16, 2, 1024),
+                                                          (1024, 16, 8, 64, 512, 8, 2, 512)):
+            att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                                    mask=dict(size=window, keep_first=0)),
+                       mlp=dict(kind="moe", expert=dict(ff=ff), router=dict(experts=E, top=top, scale=1.0)))
+            models = {
+                "voserax": dict(architecture="Voserax", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5,
+                                streams=4, max_positions=1 << 16,
+                                layers=voserax_layers(L, width, heads, kv, dim, window, E, top, ff, ff)),
+                "tifapel": dict(architecture="Tifapel", vocab=vocab, width=width, norm=dict(eps=1e-6),
+                                layers=[json.loads(json.dumps(att)) for _ in range(L)]),
+            }
+            res = _design_models(args, models, vocab, T, B, depth, rng)
+            runs.append(dict(sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, window=window, experts=E, top=top,
+                                        expert_ff=ff, shared_ff=ff, streams=4, conv=4, vocab=vocab), **res))
+        print(json.dumps(dict(design="voserax", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src, hbm_gbs=pk["hbm_gbs"],
+                              bf16_tflops=pk["bf16_tflops"], data="synthetic: seeded uniform token ids, random weights",
+                              runs=runs)))
+        return 0
+    width, heads, kv, dim, window, keep, E, top, ff = 2048, 16, 4, 128, 1024, 4, 16, 2, 1024
     models = {
         "tifapel": dict(architecture="Tifapel", vocab=vocab, width=width, norm=dict(eps=1e-6),
                         layers=tifapel_layers(L, width, heads, kv, dim, window, keep, E, top, ff, (4, 2))),
@@ -442,6 +482,20 @@ def design_bench(args) -> int:
                       num_key_value_heads=kv, head_dim=dim, intermediate_size=top * ff, vocab_size=vocab,
                       use_sliding_window=True, sliding_window=window, max_window_layers=0, eos_token_id=0),
     }
+    result = _design_models(args, models, vocab, T, B, depth, rng)
+    print(json.dumps(dict(design="tifapel", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src,
+                          hbm_gbs=pk["hbm_gbs"], bf16_tflops=pk["bf16_tflops"],
+                          sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, window=window, keep_first=keep,
+                                     experts=E, top=top, expert_ff=ff, dense_ff=top * ff, vocab=vocab),
+                          data="synthetic: seeded uniform token ids, random weights", **result)))
+    return 0
+
+
+def _design_models(args, models, vocab, T, B, depth, rng) -> dict:
+    """Per model of ``models`` (name -> raw configuration): prompt and decode times and the per-kernel lists."""
+    import torch
+
+    from llmoxide_b200 import Engine, LoadOptions, kernels, read_config
 
     def event_ms(fn):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -461,12 +515,14 @@ def design_bench(args) -> int:
 
             def call(*a):
                 tag = name.replace("llmx_", "")
-                if name.startswith("llmx_gemm_tc"):
+                if name.startswith("llmx_gemm_tc") and len(a) > 6:
                     tag += f" N{a[5]} K{a[6]}"
                 elif name == "llmx_gemm_fma":
                     tag += f" N{a[7]} K{a[8]}"
                 elif name == "llmx_moe_grouped_tc":
                     tag += " gate|up" if a[13] else " down"
+                elif name == "llmx_stream_mix_norm":
+                    tag += " update+norm" if a[7] and a[14] else " norm" if a[14] else " update"
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 code = f(*a)
@@ -529,12 +585,7 @@ def design_bench(args) -> int:
         print(f"[bench] {name}: prefill {T} tokens {pre_ms:.2f} ms, decode b{B} {dec_ms:.3f} ms/step", file=sys.stderr)
         del eng
         torch.cuda.empty_cache()
-    print(json.dumps(dict(design="tifapel", unit="tokens/s", dtype="bf16", layers=L, peaks=pk_src,
-                          hbm_gbs=pk["hbm_gbs"], bf16_tflops=pk["bf16_tflops"],
-                          sizes=dict(width=width, heads=heads, kv_heads=kv, head_dim=dim, window=window, keep_first=keep,
-                                     experts=E, top=top, expert_ff=ff, dense_ff=top * ff, vocab=vocab),
-                          data="synthetic: seeded uniform token ids, random weights", **result)))
-    return 0
+    return result
 
 
 def cpu_baseline() -> int:

@@ -441,67 +441,93 @@ LLMX_API int llmx_moe_grouped_fma(const void* X, int x_dtype, long long ldx, con
 }
 
 // ---------------------------------------------------------------------------
-// Identity experts and a gated shared expert, both written as further partials of the feed-forward's result.
+// Identity experts and a gated shared expert, both written as further partials of the feed-forward's result, in
+// one launch.
 //
-// identity: for every pair (t, choice) whose expert id is >= n_real, y[choice][t][:] = weight * x[t][:] (the
-//   expert's output is its input).  One CTA per pair; pairs of real experts are left alone.
-// row_gate: out[t][:] = gate(z[t * ldz]) * sum_p in[p][t][:], gate = sigmoid: the shared expert's result times one
-//   number per token.
+// CTAs 0 .. T*top-1, one per pair (t, choice): if the pair's expert id is >= n_real (an identity expert, whose
+//   output is its input), y[choice][t][:] = weight * x[t][:]; pairs of real experts are left alone.
+// CTAs T*top .. T*top+T-1 (with a shared expert), one per token: y[top][t][:] = sigmoid(z[t * ldz]) * sum_p
+//   shared[p][t][:], the shared expert's result times one number per token.
 // ---------------------------------------------------------------------------
-template <typename TX>
-__global__ void moe_identity_kernel(const TX* __restrict__ x, long long ldx, const int* __restrict__ ids,
-                                    const float* __restrict__ wts, float* __restrict__ y, int n_tokens, int top, int d,
-                                    int n_real) {
+template <typename TX, typename TS, int VEC>
+__global__ void __launch_bounds__(256)
+moe_extras_kernel(const TX* __restrict__ x, long long ldx, const int* __restrict__ ids, const float* __restrict__ wts,
+                  float* __restrict__ y, int n_tokens, int top, int d, int n_real, const TS* __restrict__ shared,
+                  int n_split, size_t split_stride, const float* __restrict__ z, int ldz) {
   pdl_launch_dependents();
   pdl_wait();
-  const int pair = blockIdx.x;
-  if (ids[pair] < n_real) return;
-  const int t = pair / top, choice = pair - t * top;
-  const float w = wts[pair];
-  const TX* xr = x + (size_t)t * ldx;
-  float* yr = y + ((size_t)choice * n_tokens + t) * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) yr[i] = w * to_f32(xr[i]);
-}
-
-LLMX_API int llmx_moe_identity(const void* x, int x_dtype, long long ldx, const int* ids, const float* wts, float* y,
-                               int n_tokens, int top, int d, int n_real, cudaStream_t stream) {
-  if (n_tokens <= 0) return 0;
-  if (top <= 0 || d <= 0 || ldx < d) return LLMX_REFUSED(1);
-  const dim3 grid((unsigned)n_tokens * top);
-  if (x_dtype == LLMX_F32)
-    launch_pdl(moe_identity_kernel<float>, grid, dim3(128), 0, stream, (const float*)x, ldx, ids, wts, y, n_tokens, top, d, n_real);
-  else if (x_dtype == LLMX_BF16)
-    launch_pdl(moe_identity_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)x, ldx, ids, wts, y, n_tokens, top, d, n_real);
-  else
-    return LLMX_REFUSED(2);
-  return LLMX_LAUNCH_STATUS();
-}
-
-template <typename TI>
-__global__ void moe_row_gate_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, const float* __restrict__ z,
-                                    int ldz, float* __restrict__ out, int n_tokens, int d) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int t = blockIdx.x;
+  const int n_pairs = n_tokens * top;
+  if ((int)blockIdx.x < n_pairs) {
+    const int pair = blockIdx.x;
+    if (ids[pair] < n_real) return;
+    const int t = pair / top, choice = pair - t * top;
+    const float w = wts[pair];
+    const TX* xr = x + (size_t)t * ldx;
+    float* yr = y + ((size_t)choice * n_tokens + t) * d;
+    for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
+      if (VEC == 8) {
+        float v[8];
+        moe_load8(xr + i, v);
+        *reinterpret_cast<float4*>(yr + i) = make_float4(w * v[0], w * v[1], w * v[2], w * v[3]);
+        *reinterpret_cast<float4*>(yr + i + 4) = make_float4(w * v[4], w * v[5], w * v[6], w * v[7]);
+      } else {
+        yr[i] = w * to_f32(xr[i]);
+      }
+    }
+    return;
+  }
+  const int t = blockIdx.x - n_pairs;
   const float gate = 1.0f / (1.0f + expf(-z[(size_t)t * ldz]));
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float v = 0.f;
-    for (int p = 0; p < n_split; ++p) v += to_f32(in[(size_t)p * split_stride + (size_t)t * d + i]);
-    out[(size_t)t * d + i] = gate * v;
+  float* yr = y + ((size_t)top * n_tokens + t) * d;
+  for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
+    if (VEC == 8) {
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < n_split; ++p) {
+        float a[8];
+        moe_load8(shared + (size_t)p * split_stride + (size_t)t * d + i, a);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += a[e];
+      }
+      *reinterpret_cast<float4*>(yr + i) = make_float4(gate * v[0], gate * v[1], gate * v[2], gate * v[3]);
+      *reinterpret_cast<float4*>(yr + i + 4) = make_float4(gate * v[4], gate * v[5], gate * v[6], gate * v[7]);
+    } else {
+      float v = 0.f;
+      for (int p = 0; p < n_split; ++p) v += to_f32(shared[(size_t)p * split_stride + (size_t)t * d + i]);
+      yr[i] = gate * v;
+    }
   }
 }
 
-LLMX_API int llmx_moe_row_gate(const void* in, int in_dtype, int n_split, long long split_stride, const float* z, int ldz,
-                               float* out, int n_tokens, int d, cudaStream_t stream) {
+// x [T, d] (row stride ldx); ids, wts [T, top]; y float32 [top (+1), T, d]; identity experts are ids >= n_real
+// (n_real >= all ids: none).  shared: null, or the shared expert's result [T, d] as n_split partials, with z (one
+// float per token, ldz apart) the logit of its gate.
+LLMX_API int llmx_moe_extras(const void* x, int x_dtype, long long ldx, const int* ids, const float* wts, float* y,
+                             int n_tokens, int top, int d, int n_real, const void* shared, int shared_dtype, int n_split,
+                             long long split_stride, const float* z, int ldz, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (d <= 0 || n_split < 1 || ldz < 1) return LLMX_REFUSED(1);
-  if (in_dtype == LLMX_F32)
-    launch_pdl(moe_row_gate_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)in, n_split,
-               (size_t)split_stride, z, ldz, out, n_tokens, d);
-  else if (in_dtype == LLMX_BF16)
-    launch_pdl(moe_row_gate_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const bf16*)in, n_split,
-               (size_t)split_stride, z, ldz, out, n_tokens, d);
-  else
-    return LLMX_REFUSED(2);
+  if (top <= 0 || d <= 0 || ldx < d || (shared && (!z || ldz < 1 || n_split < 1))) return LLMX_REFUSED(1);
+  const dim3 grid((unsigned)n_tokens * top + (shared ? (unsigned)n_tokens : 0u));
+  // eight columns per thread and load where every row starts on a 32-byte boundary
+  const bool vec = d % 8 == 0 && ldx % 8 == 0 && split_stride % 8 == 0 &&
+                   !(((uintptr_t)x | (uintptr_t)y | (uintptr_t)shared) & 31);
+  const int threads = d >= 2048 ? 256 : 128;
+#define GO(TX, TS)                                                                                                      \
+  do {                                                                                                                  \
+    if (vec)                                                                                                            \
+      launch_pdl(moe_extras_kernel<TX, TS, 8>, grid, dim3(threads), 0, stream, (const TX*)x, ldx, ids, wts, y, n_tokens, \
+                 top, d, n_real, (const TS*)shared, n_split, (size_t)split_stride, z, ldz);                             \
+    else                                                                                                                \
+      launch_pdl(moe_extras_kernel<TX, TS, 1>, grid, dim3(threads), 0, stream, (const TX*)x, ldx, ids, wts, y, n_tokens, \
+                 top, d, n_real, (const TS*)shared, n_split, (size_t)split_stride, z, ldz);                             \
+  } while (0)
+  const int key = x_dtype * 2 + (shared ? shared_dtype : LLMX_F32);
+  switch (key) {
+    case 0: GO(float, float); break;
+    case 1: GO(float, bf16); break;
+    case 2: GO(bf16, float); break;
+    case 3: GO(bf16, bf16); break;
+    default: return LLMX_REFUSED(2);
+  }
+#undef GO
   return LLMX_LAUNCH_STATUS();
 }

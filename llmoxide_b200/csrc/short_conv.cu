@@ -2,7 +2,8 @@
 // attention mixer does to its heads before it attends: rotation of q and k, mixing of the values with those
 // of an earlier layer, the cache write of k and v.
 //
-//   y_p[c] = sum_j w[c][j] * u_(p - taps + 1 + j)[c],   j = 0..taps-1,   u = 0 before the sequence's start
+//   y_p[c] = sum_j w[j][c] * u_(p - taps + 1 + j)[c],   j = 0..taps-1,   u = 0 before the sequence's start
+// (the weights come tap-major, [taps][C], so that a warp's lanes read neighbouring channels of one tap)
 //
 // u of the positions before the step's first token comes from the sequence's state: the last taps-1 projected
 // rows, float32 [slot][taps-1][C], oldest first (zero-filled when the slot gets its owner, which is also what
@@ -26,7 +27,43 @@ __device__ __forceinline__ float sc_value(const TIN* p, int n_split, size_t spli
   return v;
 }
 
-template <typename TIN, typename TA, typename TC>
+// Four consecutive channels at a time (the vector path of the kernel below).
+__device__ __forceinline__ void sc_load4(const float* p, float* o) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  o[0] = x.x, o[1] = x.y, o[2] = x.z, o[3] = x.w;
+}
+__device__ __forceinline__ void sc_load4(const bf16* p, float* o) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  o[0] = a.x, o[1] = a.y, o[2] = b.x, o[3] = b.y;
+}
+__device__ __forceinline__ void sc_store4(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void sc_store4(bf16* p, const float* v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+template <typename TIN>
+__device__ __forceinline__ void sc_value4(const TIN* p, int n_split, size_t split_stride, float* o) {
+  sc_load4(p, o);
+  for (int s = 1; s < n_split; ++s) {
+    float t[4];
+    sc_load4(p + (size_t)s * split_stride, t);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] += t[e];
+  }
+}
+
+// VEC: a lane takes four consecutive dims per load and store (head sizes, the rotation's half and every row
+// offset are multiples of four, all pointers 16-byte aligned); the sums run in the same order as one by one.
+// SPW: heads per warp, one after another: a prompt step's warp takes four, so that the token's indices are
+// fetched once for all of them; a step of few tokens gives every head a warp of its own.
+template <typename TIN, typename TA, typename TC, bool VEC, int SPW>
 __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split, size_t split_stride,
                                        const float* __restrict__ state, const float* __restrict__ conv_w, int taps,
                                        TA* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
@@ -35,24 +72,115 @@ __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split
                                        const int* __restrict__ seq_start, const int* __restrict__ seq_past,
                                        const int* __restrict__ seq_slot, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, int n_rot, float* __restrict__ v_first,
-                                       const float* __restrict__ v_lambda, int v_mix_mode, int H, int G, int D, int Dv) {
+                                       const float* __restrict__ v_lambda, int v_mix_mode, int H, int G, int D, int Dv,
+                                       int n_tokens, int n_seqs, int n_slots, int n_pages) {
   extern __shared__ float head_buf[];
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x;
-  const int slot_h = blockIdx.y * SC_WARPS + warp;           // which head of the fused row
-  if (slot_h >= H + 2 * G) return;
+  const int slot0 = (blockIdx.y * SC_WARPS + warp) * SPW;    // the warp's first head of the fused row
+  if (slot0 >= H + 2 * G) return;
   const size_t C = (size_t)(H + G) * D + (size_t)G * Dv;
-  const bool is_q = slot_h < H, is_k = !is_q && slot_h < H + G;
-  const int hd = (is_q || is_k) ? D : Dv;
-  const size_t c0 = (is_q || is_k) ? (size_t)slot_h * D : (size_t)(H + G) * D + (size_t)(slot_h - H - G) * Dv;
   const int b = token_seq[t], pos = token_pos[t];
-  const int p0 = seq_past[b], row0 = seq_start[b];
-  const float* st = taps > 1 ? state + (size_t)seq_slot[b] * (taps - 1) * C : nullptr;
-  const int page = is_q ? 0 : block_table[(size_t)b * table_width + pos / LLMX_PAGE];
+  // Every index that comes out of the step's arrays is checked before it addresses anything: a step buffer that
+  // does not fit the launch is reported (code 1) and the warp does nothing.
+  if (b < 0 || b >= n_seqs || pos < 0 || pos / LLMX_PAGE >= table_width) {
+    if (lane == 0) llmx_report(1);
+    return;
+  }
+  const int p0 = seq_past[b], row0 = seq_start[b], slot = seq_slot[b];
+  const int page = slot0 + SPW <= H ? 0 : block_table[(size_t)b * table_width + pos / LLMX_PAGE];
+  if (p0 < 0 || p0 > pos || row0 < 0 || row0 + (pos - p0) >= n_tokens || slot < 0 || slot >= n_slots || page < 0 ||
+      page >= n_pages) {
+    if (lane == 0) llmx_report(1);
+    return;
+  }
+  const float* st = taps > 1 ? state + (size_t)slot * (taps - 1) * C : nullptr;
   const float lam = v_mix_mode == 2 ? v_lambda[0] : 0.f;
   float* buf = head_buf + warp * max(D, Dv);
   pdl_wait();
+  for (int hs = 0; hs < SPW; ++hs) {
+  const int slot_h = slot0 + hs;                             // which head of the fused row
+  if (slot_h >= H + 2 * G) break;
+  const bool is_q = slot_h < H, is_k = !is_q && slot_h < H + G;
+  const int hd = (is_q || is_k) ? D : Dv;
+  const size_t c0 = (is_q || is_k) ? (size_t)slot_h * D : (size_t)(H + G) * D + (size_t)(slot_h - H - G) * Dv;
+  if (VEC) {
+    for (int i = lane * 4; i < hd; i += 128) {
+      const size_t c = c0 + i;
+      float y[4];
+      if (taps > 0) {
+        const float* wp = conv_w + c;                 // tap j of these four channels: wp + j * C
+        y[0] = y[1] = y[2] = y[3] = 0.f;
+        // four taps' rows are asked for together (their addresses do not depend on one another), then added in
+        // the order of the taps
+        for (int j0 = 0; j0 < taps; j0 += 4) {
+          float u[4][4];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int pp = pos - taps + 1 + j0 + jj;
+            u[jj][0] = u[jj][1] = u[jj][2] = u[jj][3] = 0.f;
+            if (j0 + jj < taps) {
+              if (pp >= p0) sc_value4(proj + (size_t)(row0 + pp - p0) * C + c, n_split, split_stride, u[jj]);
+              else if (pp >= 0) sc_load4(st + (size_t)(pp - (p0 - (taps - 1))) * C + c, u[jj]);
+            }
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            if (j0 + jj < taps) {
+              float w[4];
+              sc_load4(wp + (size_t)(j0 + jj) * C, w);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) y[e] = fmaf(w[e], u[jj][e], y[e]);
+            }
+          }
+        }
+      } else {
+        sc_value4(proj + (size_t)t * C + c, n_split, split_stride, y);
+      }
+      sc_store4(buf + i, y);
+    }
+    __syncwarp();
+    if (is_q || is_k) {
+      const int half = n_rot >> 1;
+      const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
+      const float* sv = sin_t ? sin_t + (size_t)pos * half : nullptr;
+      TA* qrow = is_q ? q_out + (size_t)t * H * D + (size_t)slot_h * D : nullptr;
+      TC* krow = is_k ? k_cache + cache_row_offset(page, slot_h - H, pos % LLMX_PAGE, G, D) : nullptr;
+      for (int i = lane * 4; i < D; i += 128) {
+        float v[4], o[4], cs[4], sn[4];
+        sc_load4(buf + i, v);
+        if (i < n_rot) {         // (i and the rotation's borders are multiples of four)
+          const bool low = i < half;
+          sc_load4(low ? buf + i + half : buf + i - half, o);
+          sc_load4(c + (low ? i : i - half), cs);
+          sc_load4(sv + (low ? i : i - half), sn);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = low ? v[e] * cs[e] - o[e] * sn[e] : v[e] * cs[e] + o[e] * sn[e];
+        }
+        if (is_q) sc_store4(qrow + i, v);
+        else sc_store4(krow + i, v);
+      }
+    } else {
+      const int g = slot_h - H - G;
+      TC* vrow = v_cache + cache_row_offset(page, g, pos % LLMX_PAGE, G, Dv);
+      float* first = v_mix_mode ? v_first + (size_t)t * G * Dv + (size_t)g * Dv : nullptr;
+      for (int i = lane * 4; i < Dv; i += 128) {
+        float v[4], f[4];
+        sc_load4(buf + i, v);
+        if (v_mix_mode == 1) {
+          sc_store4(first + i, v);
+        } else if (v_mix_mode == 2) {
+          sc_load4(first + i, f);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = (1.0f - lam) * v[e] + lam * f[e];
+        }
+        sc_store4(vrow + i, v);
+      }
+    }
+    __syncwarp();      // buf is filled again for the warp's next head
+    continue;
+  }
   for (int i = lane; i < hd; i += 32) {
     const size_t c = c0 + i;
     float y;
@@ -63,7 +191,7 @@ __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split
         float u = 0.f;
         if (pp >= p0) u = sc_value(proj + (size_t)(row0 + pp - p0) * C + c, n_split, split_stride);
         else if (pp >= 0) u = st[(size_t)(pp - (p0 - (taps - 1))) * C + c];
-        y = fmaf(conv_w[c * taps + j], u, y);
+        y = fmaf(conv_w[(size_t)j * C + c], u, y);
       }
     } else {
       y = sc_value(proj + (size_t)t * C + c, n_split, split_stride);
@@ -95,6 +223,8 @@ __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split
       vrow[i] = from_f32<TC>(v);
     }
   }
+  __syncwarp();        // buf is filled again for the warp's next head
+  }
 }
 
 // One thread per (sequence, channel): the state's rows become the projected rows of the last taps-1 positions
@@ -102,15 +232,20 @@ __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split
 template <typename TIN>
 __global__ void conv_state_update_kernel(const TIN* __restrict__ proj, int n_split, size_t split_stride,
                                          float* __restrict__ state, int taps, const int* __restrict__ seq_start,
-                                         const int* __restrict__ seq_slot, int n_seqs, size_t C) {
+                                         const int* __restrict__ seq_slot, int n_seqs, size_t C, int n_tokens,
+                                         int n_slots) {
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.y;
   const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C || b >= n_seqs) return;
-  const int row0 = seq_start[b], n_new = seq_start[b + 1] - row0;
+  const int row0 = seq_start[b], n_new = seq_start[b + 1] - row0, slot = seq_slot[b];
+  if (row0 < 0 || n_new < 0 || row0 + n_new > n_tokens || slot < 0 || slot >= n_slots) {
+    if (c == 0) llmx_report(2);
+    return;
+  }
   const int keep = taps - 1;
-  float* st = state + (size_t)seq_slot[b] * keep * C + c;
+  float* st = state + (size_t)slot * keep * C + c;
   float nv[SC_MAX_TAPS];
 #pragma unroll
   for (int i = 0; i < SC_MAX_TAPS; ++i) {
@@ -125,7 +260,7 @@ __global__ void conv_state_update_kernel(const TIN* __restrict__ proj, int n_spl
   }
 }
 
-// proj [T, C] or n_split float32 partials; conv_w float32 [C, taps] (taps 0: no convolution); state float32
+// proj [T, C] or n_split float32 partials; conv_w float32 [taps, C] (taps 0: no convolution); state float32
 // [slots, taps-1, C]; q_out [T, H*D]; cos/sin float32 [positions, n_rot/2]; v_first float32 [T, G*Dv] (v_mix_mode
 // 1: written, 2: read with the weight *v_lambda).
 LLMX_API int llmx_conv_rope_cache(const void* proj, int in_dtype, int n_split, long long split_stride, const float* state,
@@ -133,7 +268,8 @@ LLMX_API int llmx_conv_rope_cache(const void* proj, int in_dtype, int n_split, l
                                   int cache_dtype, const int* block_table, int table_width, const int* token_seq,
                                   const int* token_pos, const int* seq_start, const int* seq_past, const int* seq_slot,
                                   const float* cos_t, const float* sin_t, int n_rot, float* v_first, const float* v_lambda,
-                                  int v_mix_mode, int n_tokens, int H, int G, int D, int Dv, cudaStream_t stream) {
+                                  int v_mix_mode, int n_tokens, int H, int G, int D, int Dv, int n_seqs, int n_slots,
+                                  long long n_pages, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || G <= 0 || D <= 0 || Dv <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1 || taps < 0 ||
       taps > SC_MAX_TAPS || v_mix_mode < 0 || v_mix_mode > 2)
@@ -144,12 +280,26 @@ LLMX_API int llmx_conv_rope_cache(const void* proj, int in_dtype, int n_split, l
   const int hd = D > Dv ? D : Dv;
   const size_t smem = (size_t)SC_WARPS * hd * sizeof(float);
   if (smem > 48 * 1024) return LLMX_REFUSED(3);
-  dim3 grid(n_tokens, (H + 2 * G + SC_WARPS - 1) / SC_WARPS);
-#define CASE(TIN, TA, TC)                                                                                            \
-  launch_pdl(conv_rope_cache_kernel<TIN, TA, TC>, grid, dim3(SC_WARPS * 32), smem, stream, (const TIN*)proj, n_split, \
+  const int spw = n_tokens > 64 ? 4 : 1;
+  dim3 grid(n_tokens, (H + 2 * G + SC_WARPS * spw - 1) / (SC_WARPS * spw));
+  const bool vec = D % 4 == 0 && Dv % 4 == 0 && n_rot % 8 == 0 && split_stride % 4 == 0 &&
+                   !(((uintptr_t)proj | (uintptr_t)state | (uintptr_t)conv_w | (uintptr_t)q_out | (uintptr_t)k_cache |
+                      (uintptr_t)v_cache | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)v_first) & 15);
+#define GO(TIN, TA, TC, VEC)              \
+  do {                                    \
+    if (spw == 4) GO2(TIN, TA, TC, VEC, 4); \
+    else GO2(TIN, TA, TC, VEC, 1);        \
+  } while (0)
+#define GO2(TIN, TA, TC, VEC, SPW)                                                                                      \
+  launch_pdl(conv_rope_cache_kernel<TIN, TA, TC, VEC, SPW>, grid, dim3(SC_WARPS * 32), smem, stream, (const TIN*)proj, n_split, \
              (size_t)split_stride, state, conv_w, taps, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,           \
              table_width, token_seq, token_pos, seq_start, seq_past, seq_slot, cos_t, sin_t, n_rot, v_first, v_lambda, \
-             v_mix_mode, H, G, D, Dv)
+             v_mix_mode, H, G, D, Dv, n_tokens, n_seqs, n_slots, (int)n_pages)
+#define CASE(TIN, TA, TC)              \
+  do {                                 \
+    if (vec) GO(TIN, TA, TC, true);    \
+    else GO(TIN, TA, TC, false);       \
+  } while (0)
   const int key = in_dtype * 4 + act_dtype * 2 + cache_dtype;
   switch (key) {
     case 0: CASE(float, float, float); break;
@@ -161,21 +311,23 @@ LLMX_API int llmx_conv_rope_cache(const void* proj, int in_dtype, int n_split, l
     default: return LLMX_REFUSED(2);
   }
 #undef CASE
+#undef GO
+#undef GO2
   return LLMX_LAUNCH_STATUS();
 }
 
 LLMX_API int llmx_conv_state_update(const void* proj, int in_dtype, int n_split, long long split_stride, float* state,
                                     int taps, const int* seq_start, const int* seq_slot, int n_seqs, long long C,
-                                    cudaStream_t stream) {
+                                    int n_tokens, int n_slots, cudaStream_t stream) {
   if (n_seqs <= 0 || taps <= 1) return 0;
   if (taps > SC_MAX_TAPS || C <= 0 || n_split < 1 || n_seqs > 65535) return LLMX_REFUSED(1);
   dim3 grid((unsigned)((C + 127) / 128), n_seqs);
   if (in_dtype == LLMX_F32)
     launch_pdl(conv_state_update_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, n_split,
-               (size_t)split_stride, state, taps, seq_start, seq_slot, n_seqs, (size_t)C);
+               (size_t)split_stride, state, taps, seq_start, seq_slot, n_seqs, (size_t)C, n_tokens, n_slots);
   else if (in_dtype == LLMX_BF16)
     launch_pdl(conv_state_update_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)proj, n_split,
-               (size_t)split_stride, state, taps, seq_start, seq_slot, n_seqs, (size_t)C);
+               (size_t)split_stride, state, taps, seq_start, seq_slot, n_seqs, (size_t)C, n_tokens, n_slots);
   else
     return LLMX_REFUSED(2);
   return LLMX_LAUNCH_STATUS();

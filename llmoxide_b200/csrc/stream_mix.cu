@@ -13,17 +13,55 @@
 //     out[r][i] = u / sqrt(mean_i(u^2) + eps) * gain[i]      (out == nullptr: only the update)
 //
 // Everything is float32 and every sum runs in an order fixed by (s, p, i) alone: a row's result does not depend
-// on the batch.  One CTA per row; u is staged in shared memory between the two passes.
+// on the batch.  One CTA per row, four columns per thread and load where the rows' alignment allows; u is staged
+// in shared memory between the two passes.
 #include "common.cuh"
 
 #define SM_MAX_STREAMS 8
 
-template <typename TD, typename TO>
-__global__ void __launch_bounds__(256)
+// Four columns at a time (d a multiple of 4: every row then starts on a 16-byte boundary), or one (VEC == 1).
+template <int VEC> struct SmVec;
+template <> struct SmVec<1> {
+  float v[1];
+};
+template <> struct SmVec<4> {
+  float v[4];
+};
+__device__ __forceinline__ void sm_load(const float* p, SmVec<1>& o) { o.v[0] = p[0]; }
+__device__ __forceinline__ void sm_load(const bf16* p, SmVec<1>& o) { o.v[0] = __bfloat162float(p[0]); }
+__device__ __forceinline__ void sm_load(const float* p, SmVec<4>& o) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  o.v[0] = x.x, o.v[1] = x.y, o.v[2] = x.z, o.v[3] = x.w;
+}
+__device__ __forceinline__ void sm_load(const bf16* p, SmVec<4>& o) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  o.v[0] = a.x, o.v[1] = a.y, o.v[2] = b.x, o.v[3] = b.y;
+}
+__device__ __forceinline__ void sm_store(float* p, const SmVec<1>& o) { p[0] = o.v[0]; }
+__device__ __forceinline__ void sm_store(bf16* p, const SmVec<1>& o) { p[0] = __float2bfloat16_rn(o.v[0]); }
+__device__ __forceinline__ void sm_store(float* p, const SmVec<4>& o) {
+  *reinterpret_cast<float4*>(p) = make_float4(o.v[0], o.v[1], o.v[2], o.v[3]);
+}
+__device__ __forceinline__ void sm_store(bf16* p, const SmVec<4>& o) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(o.v[0], o.v[1]), b = __floats2bfloat162_rn(o.v[2], o.v[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+#define SM_MAX_PARTS 4      // partials whose loads go out together with the copies' (more are added one by one)
+
+// MAXS: the most copies this instance takes (its arrays live in registers: a kernel for eight copies that is
+// handed four would hold twice the registers it needs and halve the CTAs per SM).
+template <typename TD, typename TO, int VEC, int MAXS>
+__global__ void __launch_bounds__(512)
 stream_mix_norm_kernel(float* __restrict__ h, size_t stream_stride, int S, const TD* __restrict__ delta, int n_split,
                        size_t split_stride, const float* __restrict__ mix, const float* __restrict__ write,
                        const float* __restrict__ read, const int* __restrict__ rows, const float* __restrict__ gain,
-                       float eps, TO* __restrict__ out, int d, int write_h) {
+                       float eps, TO* __restrict__ out, int d, int write_h, int n_tokens) {
   extern __shared__ float u_buf[];   // [d]
   __shared__ float red[32];
   __shared__ float w_mix[SM_MAX_STREAMS * SM_MAX_STREAMS], w_write[SM_MAX_STREAMS], w_read[SM_MAX_STREAMS];
@@ -38,71 +76,118 @@ stream_mix_norm_kernel(float* __restrict__ h, size_t stream_stride, int S, const
     w_read[threadIdx.x] = read ? read[threadIdx.x] : 1.0f;
   }
   __syncthreads();
+  if (t < 0 || t >= n_tokens) {        // a row index that does not fit the stream: reported, nothing is touched
+    if (threadIdx.x == 0) llmx_report(1);
+    return;
+  }
   pdl_wait();
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float x[SM_MAX_STREAMS];
+  for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
+    // every load of this thread's columns goes out before the first is used: the copies, then the partials
+    SmVec<VEC> x[MAXS], part[SM_MAX_PARTS];
 #pragma unroll
-    for (int s = 0; s < SM_MAX_STREAMS; ++s)
-      if (s < S) x[s] = h[(size_t)s * stream_stride + (size_t)t * d + i];
-    if (update) {
-      float y = 0.f;
-      if (delta) {
-        const TD* p = delta + (size_t)t * d + i;
-        for (int sp = 0; sp < n_split; ++sp) y += to_f32(p[(size_t)sp * split_stride]);
-      }
-      float nx[SM_MAX_STREAMS];
+    for (int s = 0; s < MAXS; ++s)
+      if (s < S) sm_load(h + (size_t)s * stream_stride + (size_t)t * d + i, x[s]);
+    const TD* p = (update && delta) ? delta + (size_t)t * d + i : nullptr;
+    if (p) {
 #pragma unroll
-      for (int to = 0; to < SM_MAX_STREAMS; ++to) {
-        if (to >= S) break;
-        float acc = 0.f;
+      for (int sp = 0; sp < SM_MAX_PARTS; ++sp)
+        if (sp < n_split) sm_load(p + (size_t)sp * split_stride, part[sp]);
+    }
+    SmVec<VEC> u;
 #pragma unroll
-        for (int s = 0; s < SM_MAX_STREAMS; ++s)
-          if (s < S) acc = fmaf(w_mix[s * S + to], x[s], acc);
-        nx[to] = fmaf(w_write[to], y, acc);
-      }
+    for (int e = 0; e < VEC; ++e) {
+      if (update) {
+        float y = 0.f;
+        if (p) {
 #pragma unroll
-      for (int s = 0; s < SM_MAX_STREAMS; ++s)
-        if (s < S) {
-          x[s] = nx[s];
-          if (write_h) h[(size_t)s * stream_stride + (size_t)t * d + i] = nx[s];
+          for (int sp = 0; sp < SM_MAX_PARTS; ++sp)
+            if (sp < n_split) y += part[sp].v[e];
         }
-    }
-    if (out) {
-      float u = 0.f;
+        float nx[MAXS];
 #pragma unroll
-      for (int s = 0; s < SM_MAX_STREAMS; ++s)
-        if (s < S) u = fmaf(w_read[s], x[s], u);
-      u_buf[i] = u;
-      ss += u * u;
+        for (int to = 0; to < MAXS; ++to) {
+          if (to >= S) break;
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < MAXS; ++s)
+            if (s < S) acc = fmaf(w_mix[s * S + to], x[s].v[e], acc);
+          nx[to] = acc;
+        }
+        if (p) {          // partials beyond the first few, in order, before the result joins the copies
+          for (int sp = SM_MAX_PARTS; sp < n_split; ++sp) y += to_f32(p[(size_t)sp * split_stride + e]);
+        }
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s)
+          if (s < S) x[s].v[e] = fmaf(w_write[s], y, nx[s]);
+      }
+      float uu = 0.f;
+#pragma unroll
+      for (int s = 0; s < MAXS; ++s)
+        if (s < S) uu = fmaf(w_read[s], x[s].v[e], uu);
+      u.v[e] = uu;
+      ss += uu * uu;
     }
+    if (update && write_h) {
+#pragma unroll
+      for (int s = 0; s < MAXS; ++s)
+        if (s < S) sm_store(h + (size_t)s * stream_stride + (size_t)t * d + i, x[s]);
+    }
+    if (out) sm_store(u_buf + i, u);
   }
   if (!out) return;
   const float total = block_sum(ss, red);
   const float scale = 1.0f / sqrtf(total / (float)d + eps);
   TO* orow = out + (size_t)r * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) orow[i] = from_f32<TO>((u_buf[i] * scale) * gain[i]);
+  for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
+    SmVec<VEC> u, g;
+    sm_load(u_buf + i, u);
+    sm_load(gain + i, g);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) u.v[e] = (u.v[e] * scale) * g.v[e];
+    sm_store(orow + i, u);
+  }
 }
 
 // h float32 [S, T, d] (copy s at h + s * stream_stride).  delta: null, or n_split partials [T, d] (split_stride
 // apart).  mix [S*S] (from, to) and write [S]: the update to apply first, or null for none.  read [S] or null
-// (all ones).  rows: null or n_rows row indices.  out: null or [n_rows, d].
+// (all ones).  rows: null or n_rows row indices into the n_tokens rows of a copy.  out: null or [n_rows, d].
 LLMX_API int llmx_stream_mix_norm(float* h, long long stream_stride, int S, const void* delta, int delta_dtype,
                                   int n_split, long long split_stride, const float* mix, const float* write,
                                   const float* read, const int* rows, int n_rows, const float* gain, float eps,
-                                  void* out, int out_dtype, int d, int write_h, cudaStream_t stream) {
+                                  void* out, int out_dtype, int d, int write_h, int n_tokens, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (S <= 0 || S > SM_MAX_STREAMS || d <= 0 || n_split < 1) return LLMX_REFUSED(1);
   if ((mix == nullptr) != (write == nullptr) || (delta && !mix) || (out && !gain)) return LLMX_REFUSED(4);
   const size_t smem = out ? (size_t)d * sizeof(float) : 0;
   if (smem > 200 * 1024) return LLMX_REFUSED(3);
-#define CASE(TD, TO)                                                                                              \
-  do {                                                                                                            \
-    if (smem > 48 * 1024)                                                                                         \
-      cudaFuncSetAttribute(stream_mix_norm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    launch_pdl(stream_mix_norm_kernel<TD, TO>, dim3(n_rows), dim3(256), smem, stream, h, (size_t)stream_stride, S, \
-               (const TD*)delta, n_split, (size_t)split_stride, mix, write, read, rows, gain, eps, (TO*)out, d,    \
-               write_h);                                                                                          \
+  // four columns per load where every row starts on a 16-byte boundary (8 bytes for bfloat16 rows)
+  const bool vec = d % 4 == 0 && stream_stride % 4 == 0 && split_stride % 4 == 0 &&
+                   !(((uintptr_t)h | (uintptr_t)delta | (uintptr_t)out | (uintptr_t)gain) & 15);
+  // a step of few rows leaves most SMs idle: every row then gets up to 512 threads, so that one pass of loads
+  // covers it; a prompt's rows take 256 each and several share an SM
+  const int threads = (n_rows <= 64 && d > 1024) ? 512 : 256;
+#define GO(TD, TO, VEC, MAXS)                                                                                          \
+  do {                                                                                                                 \
+    auto kernel = stream_mix_norm_kernel<TD, TO, VEC, MAXS>;                                                           \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+    launch_pdl(kernel, dim3(n_rows), dim3(threads), smem, stream, h, (size_t)stream_stride, S, (const TD*)delta, n_split,  \
+               (size_t)split_stride, mix, write, read, rows, gain, eps, (TO*)out, d, write_h, n_tokens);               \
+  } while (0)
+  // up to four copies: four columns per load where the alignment allows; five to eight: one column (registers)
+#define CASE(TD, TO)                          \
+  do {                                        \
+    if (S > 4) GO(TD, TO, 1, 8);              \
+    else if (S > 2) {                         \
+      if (vec) GO(TD, TO, 4, 4);              \
+      else GO(TD, TO, 1, 4);                  \
+    } else if (S == 2) {                      \
+      if (vec) GO(TD, TO, 4, 2);              \
+      else GO(TD, TO, 1, 2);                  \
+    } else {                                  \
+      if (vec) GO(TD, TO, 4, 1);              \
+      else GO(TD, TO, 1, 1);                  \
+    }                                         \
   } while (0)
   if (delta_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
   else if (delta_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
@@ -110,5 +195,6 @@ LLMX_API int llmx_stream_mix_norm(float* h, long long stream_stride, int S, cons
   else if (delta_dtype == LLMX_BF16 && out_dtype == LLMX_F32) CASE(bf16, float);
   else return LLMX_REFUSED(2);
 #undef CASE
+#undef GO
   return LLMX_LAUNCH_STATUS();
 }

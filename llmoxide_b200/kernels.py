@@ -121,7 +121,8 @@ def _library(lib_name: str):
 # or a request a kernel could not serve, leaves a code there.  The host looks at the words whenever it has
 # waited for a step anyway (no copy, no extra synchronisation).
 
-_STATUS_SLOTS = {"gemm_tc": 0, "attention_prefill_tc": 1, "attention_decode": 2, "sampling": 3, "moe_tc": 4}
+_STATUS_SLOTS = {"gemm_tc": 0, "attention_prefill_tc": 1, "attention_decode": 2, "sampling": 3, "moe_tc": 4,
+                 "short_conv": 5, "stream_mix": 6}
 _STATUS_MEANING = {
     "gemm_tc": {1: "the producer's wait for a free stage ran out", 2: "the MMA issuer's wait for a stage's data ran out",
                 3: "the epilogue's wait for an accumulator ran out", 4: "the MMA issuer's wait for a drained accumulator ran out",
@@ -133,6 +134,9 @@ _STATUS_MEANING = {
                3: "the epilogue's wait for an accumulator ran out", 4: "the MMA issuer's wait for a drained accumulator ran out"},
     "attention_decode": {1: "a copy into shared memory never completed", 2: "its shared memory is not 1024-byte aligned"},
     "sampling": {1: "top_p < 1 over more candidates than the kernel sorts", 2: "top_k beyond what the kernel sorts"},
+    "short_conv": {1: "a token's sequence, position, slot or page lies outside the launch's arrays",
+                   2: "a sequence's rows or slot lie outside the launch's arrays (state update)"},
+    "stream_mix": {1: "a wanted row lies outside the stream"},
 }
 _status_host = None
 
@@ -266,16 +270,16 @@ def stream_mix_norm(h, delta, mix, write, read, gain, eps: float, out, rows=None
         assert out.shape[0] >= n_rows and out.shape[-1] == d and gain.dtype == torch.float32
     f = _fn("stream_mix", "llmx_stream_mix_norm",
             [c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-             c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+             c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(h), h.stride(0), S, _ptr(delta), dtag, n_split, stride, _ptr(mix), _ptr(write), _ptr(read), _ptr(rows),
-             n_rows, _ptr(gain), eps, _ptr(out), _tag(out) if out is not None else F32, d, int(write_h), _stream()),
+             n_rows, _ptr(gain), eps, _ptr(out), _tag(out) if out is not None else F32, d, int(write_h), T, _stream()),
            "stream_mix_norm")
 
 
 def conv_rope_cache(proj, state, conv_w, taps: int, q_out, k_cache, v_cache, block_table, ctx, cos, sin, n_rot: int,
                     v_first, v_lambda, v_mix_mode: int, n_heads: int, n_kv_heads: int, head_dim: int,
                     v_head_dim: int) -> None:
-    """A short causal convolution (``conv_w`` float32 [C, taps]; taps 0: none) over the fused q|k|v projection
+    """A short causal convolution (``conv_w`` float32 [taps, C], tap-major; taps 0: none) over the fused q|k|v projection
     ``proj`` ([T,C] or float32 partials [P,T,C]) with the sequences' earlier rows from ``state`` float32
     [slots, taps-1, C]; then q and k rotated (q to ``q_out`` [T,H*D], k to the cache) and v written to the cache:
     as it is (``v_mix_mode`` 0), also copied to ``v_first`` float32 [T,G*Dv] (1), or mixed with it as
@@ -288,7 +292,7 @@ def conv_rope_cache(proj, state, conv_w, taps: int, q_out, k_cache, v_cache, blo
     assert proj.shape[-1] == C and q_out.shape == (T, n_heads * head_dim)
     assert k_cache.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
     if taps:
-        assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and conv_w.is_contiguous()
+        assert conv_w.dtype == torch.float32 and conv_w.shape == (taps, C) and conv_w.is_contiguous()
     if taps > 1:
         assert state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C) and state.is_contiguous()
     if v_mix_mode:
@@ -296,12 +300,12 @@ def conv_rope_cache(proj, state, conv_w, taps: int, q_out, k_cache, v_cache, blo
     f = _fn("short_conv", "llmx_conv_rope_cache",
             [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p])
     _check(f(_ptr(proj), _tag(proj), n_split, stride, _ptr(state), _ptr(conv_w), taps, _ptr(q_out), _tag(q_out),
              _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table), block_table.shape[1], _ptr(ctx.token_seq),
              _ptr(ctx.token_pos), _ptr(ctx.seq_start), _ptr(ctx.seq_past), _ptr(ctx.seq_slot), _ptr(cos), _ptr(sin), n_rot,
-             _ptr(v_first), _ptr(v_lambda), v_mix_mode, T, n_heads, n_kv_heads, head_dim, v_head_dim, _stream()),
-           "conv_rope_cache")
+             _ptr(v_first), _ptr(v_lambda), v_mix_mode, T, n_heads, n_kv_heads, head_dim, v_head_dim, ctx.n_seqs,
+             state.shape[0] if state is not None else 1 << 30, k_cache.shape[0], _stream()), "conv_rope_cache")
 
 
 def conv_state_update(proj, state, taps: int, ctx) -> None:
@@ -314,9 +318,9 @@ def conv_state_update(proj, state, taps: int, ctx) -> None:
     C = proj.shape[-1]
     assert state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C) and state.is_contiguous()
     f = _fn("short_conv", "llmx_conv_state_update",
-            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
     _check(f(_ptr(proj), _tag(proj), n_split, stride, _ptr(state), taps, _ptr(ctx.seq_start), _ptr(ctx.seq_slot),
-             ctx.n_seqs, C, _stream()), "conv_state_update")
+             ctx.n_seqs, C, proj.shape[-2], state.shape[0], _stream()), "conv_state_update")
 
 
 def softcap(x: torch.Tensor, cap: float) -> None:
@@ -938,29 +942,27 @@ def moe_grouped(x, w, y, perm, tiles, pair_weight, top: int, n_tokens: int, gate
              _ptr(pair_weight), top, n_tokens, N, K, int(gated), *gate_act_args(activation), _stream()), "moe_grouped")
 
 
-def moe_identity(x, ids, weights, y, n_real: int) -> None:
-    """y[choice, t, :] = weights[t, choice] * x[t, :] for every pair whose expert id is ``n_real`` or more (an
-    identity expert's output is its input); the other pairs' rows are left alone.  y float32 [top, T, d]."""
-    _dev(x, ids, weights, y)
+def moe_extras(x, ids, weights, y, n_real: int, shared=None, shared_z=None) -> None:
+    """What the grouped products leave out, in one launch.  Identity experts: y[choice, t, :] = weights[t, choice] *
+    x[t, :] for every pair whose expert id is ``n_real`` or more (an identity expert's output is its input); the other
+    pairs' rows are left alone.  A shared expert: y[top, t, :] = sigmoid(shared_z[t]) * shared[t, :] (``shared``
+    [T, d] or partials [P, T, d]; ``shared_z`` float32, one number per token, a column of a wider row allowed).
+    y float32 [top (+1), T, d]."""
+    _dev(x, ids, weights, y, shared, shared_z)
     _contig("ids", ids), _contig("weights", weights), _contig("y", y)
     T, top = ids.shape
-    assert x.stride(1) == 1 and y.dtype == torch.float32 and y.shape[-2:] == (T, x.shape[1]) and y.shape[0] >= top
-    f = _fn("moe", "llmx_moe_identity",
-            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(ids), _ptr(weights), _ptr(y), T, top, x.shape[1], n_real, _stream()),
-           "moe_identity")
-
-
-def moe_row_gate(parts, z, out) -> None:
-    """out[t, :] = sigmoid(z[t]) * sum_p parts[p, t, :]; ``parts`` [T, d] or partials [P, T, d]; ``z`` float32, one
-    number per token (a column of a wider row: its stride is taken); ``out`` float32 [T, d]."""
-    _dev(parts, z, out)
-    _contig("parts", parts), _contig("out", out)
-    if parts.dim() == 2:
-        parts = parts.unsqueeze(0)
-    assert out.dtype == torch.float32 and parts.shape[1:] == out.shape and z.dtype == torch.float32
-    assert z.dim() == 1 and z.numel() == out.shape[0]
-    f = _fn("moe", "llmx_moe_row_gate",
-            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
-    _check(f(_ptr(parts), _tag(parts), parts.shape[0], parts.stride(0), _ptr(z), z.stride(0), _ptr(out), out.shape[0],
-             out.shape[1], _stream()), "moe_row_gate")
+    d = x.shape[1]
+    assert x.stride(1) == 1 and y.dtype == torch.float32 and y.shape[-2:] == (T, d)
+    assert y.shape[0] >= top + (1 if shared is not None else 0)
+    n_split, stride, stag, ldz = 1, 0, F32, 1
+    if shared is not None:
+        _contig("shared", shared)
+        if shared.dim() == 2:
+            shared = shared.unsqueeze(0)
+        assert shared.shape[1:] == (T, d) and shared_z.dtype == torch.float32 and shared_z.dim() == 1 and shared_z.numel() == T
+        n_split, stride, stag, ldz = shared.shape[0], shared.stride(0), _tag(shared), shared_z.stride(0)
+    f = _fn("moe", "llmx_moe_extras",
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+             c_longlong, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(x), _tag(x), x.stride(0), _ptr(ids), _ptr(weights), _ptr(y), T, top, d, n_real, _ptr(shared), stag,
+             n_split, stride, _ptr(shared_z), ldz, _stream()), "moe_extras")

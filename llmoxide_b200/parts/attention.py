@@ -88,8 +88,9 @@ class GQAttention:
         if self.taps:
             if not self.own_kv or self.q_gain is not None:
                 raise Unsupported("the short convolution is built for a layer with its own keys and values and no q/k norm")
+            # [channels of q | k | v, taps] -> tap-major [taps, channels]: a warp reads neighbouring channels of a tap
             self.conv_w = torch.cat([weights.pop(t[r].name).to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")],
-                                    dim=0).contiguous()
+                                    dim=0).t().contiguous()
         if self.v_mix:
             lam = weights.pop(t["v_mix"].name).to(torch.float32).reshape(1).contiguous()
             self.v_lambda = lam if self.v_mix == "mix" else None      # the source's own weight is unused

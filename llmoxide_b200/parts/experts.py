@@ -32,7 +32,6 @@ import torch
 
 from .. import kernels
 from ..errors import ConfigError, Unsupported
-from .linear import Linear
 from .registry import register_feed_forward
 
 
@@ -82,12 +81,13 @@ class RoutedExperts:
             # the shared expert's gate reads the same rows as the router: its vector is one more row of that matrix
             self.router = torch.cat([self.router, weights.pop(t["shared_sg"].name).to(torch.float32).reshape(1, -1)],
                                     dim=0).contiguous()
-            wg, wu = weights.pop(t["shared_gate"].name), weights.pop(t["shared_up"].name)
-            self.shared_gate_up = Linear(torch.cat([wg, wu], dim=0), rt)
-            self.shared_down = Linear(weights.pop(t["shared_down"].name), rt)
-            self.shared_size = int(spec["shared_size"])
-            self.shared_activation = act(spec.get("shared_limit", spec.get("act_limit", 0.0)))
-            self.shared = True
+            # the shared expert itself is a gated feed-forward of this package, with the experts' activation
+            from ..config.spec import PartSpec
+            from .feed_forward import GatedMLP
+            self.shared = GatedMLP(PartSpec("gated_mlp", dict(
+                hidden_size=spec["hidden_size"], intermediate_size=int(spec["shared_size"]),
+                activation=act(spec.get("shared_limit", spec.get("act_limit", 0.0)))),
+                dict(gate=t["shared_gate"], up=t["shared_up"], down=t["shared_down"])), weights, rt)
         dt = rt.act_dtype
         gate_up = [torch.cat([weights.pop(t[f"gate{e}"].name), weights.pop(t[f"up{e}"].name)], dim=0).to(dt)
                    for e in range(self.E)]
@@ -102,7 +102,7 @@ class RoutedExperts:
     def libraries(self) -> set:
         libs = {"moe", "elementwise"} | ({"moe_tc"} if self.tensor_cores else set())
         if self.shared:
-            libs |= self.shared_gate_up.libraries() | self.shared_down.libraries()
+            libs |= self.shared.libraries()
         return libs
 
     def tile_rows(self, n_pairs: int) -> int:
@@ -140,12 +140,9 @@ class RoutedExperts:
             kernels.moe_grouped(x, self.gate_up, act, perm, tiles, pair_w, self.top, T, gated=True,
                                 activation=self.activation)
             kernels.moe_grouped(act, self.down, y, perm, tiles, pair_w, self.top, T, gated=False)
-        if self.n_identity:
-            # an identity expert's output is the token's own row, times the weight
-            kernels.moe_identity(x, ids, pair_w, y, self.E)
-        if self.shared:
-            gu = self.shared_gate_up(x, splits_ok=True)
-            sact = torch.empty((T, self.shared_size), dtype=self.rt.act_dtype, device=dev)
-            kernels.silu_gate(gu, sact, 0, self.shared_activation)
-            kernels.moe_row_gate(self.shared_down(sact, splits_ok=True), shared_z[:, 0], y[self.top])
+        if self.n_identity or self.shared:
+            # an identity expert's output is the token's own row times the weight; the shared expert's result is
+            # weighted by its gate: both join y in one launch
+            shared = self.shared.forward(x, ctx) if self.shared else None
+            kernels.moe_extras(x, ids, pair_w, y, self.E, shared, shared_z[:, 0] if self.shared else None)
         return y
