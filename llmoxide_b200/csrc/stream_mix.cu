@@ -80,6 +80,18 @@ stream_mix_norm_kernel(float* __restrict__ h, size_t stream_stride, int S, const
     if (threadIdx.x == 0) llmx_report(1);
     return;
   }
+  // the connection weights in registers (one shared-memory read each, not one per column)
+  // for up to four copies; more stay in shared memory, or the kernel would spill
+  constexpr bool REGW = MAXS <= 4;
+  constexpr int RW = REGW ? MAXS : 1;
+  float r_mix[RW][RW], r_write[RW], r_read[RW];
+#pragma unroll
+  for (int s = 0; s < RW; ++s) {
+    r_write[s] = s < S ? w_write[s] : 0.f;
+    r_read[s] = s < S ? w_read[s] : 0.f;
+#pragma unroll
+    for (int to = 0; to < RW; ++to) r_mix[s][to] = (s < S && to < S) ? w_mix[s * S + to] : 0.f;
+  }
   pdl_wait();
   float ss = 0.f;
   for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
@@ -111,7 +123,7 @@ stream_mix_norm_kernel(float* __restrict__ h, size_t stream_stride, int S, const
           float acc = 0.f;
 #pragma unroll
           for (int s = 0; s < MAXS; ++s)
-            if (s < S) acc = fmaf(w_mix[s * S + to], x[s].v[e], acc);
+            if (s < S) acc = fmaf(REGW ? r_mix[REGW ? s : 0][REGW ? to : 0] : w_mix[s * S + to], x[s].v[e], acc);
           nx[to] = acc;
         }
         if (p) {          // partials beyond the first few, in order, before the result joins the copies
@@ -119,12 +131,12 @@ stream_mix_norm_kernel(float* __restrict__ h, size_t stream_stride, int S, const
         }
 #pragma unroll
         for (int s = 0; s < MAXS; ++s)
-          if (s < S) x[s].v[e] = fmaf(w_write[s], y, nx[s]);
+          if (s < S) x[s].v[e] = fmaf(REGW ? r_write[REGW ? s : 0] : w_write[s], y, nx[s]);
       }
       float uu = 0.f;
 #pragma unroll
       for (int s = 0; s < MAXS; ++s)
-        if (s < S) uu = fmaf(w_read[s], x[s].v[e], uu);
+        if (s < S) uu = fmaf(REGW ? r_read[REGW ? s : 0] : w_read[s], x[s].v[e], uu);
       u.v[e] = uu;
       ss += uu * uu;
     }
