@@ -563,6 +563,7 @@ def _design_models(args, models, vocab, T, B, depth, rng) -> dict:
         for _ in range(3):
             prefill_once()
         pre_ms = statistics.median(event_ms(prefill_once) for _ in range(5))
+        eng.check_status()
         s = eng.acquire()
         pre_kernels = per_kernel(eng, [(s, rng.integers(0, vocab, T).tolist())])
         eng.release(s)

@@ -65,7 +65,7 @@ class VoseraxConfig:
     layers: list                       # as in config.json: dicts with type / mixer / mlp
     residual_mult: float = 1.0
     streams: int = 0                   # 0: no hyper-connections (one stream, plain residual sums)
-    max_positions: int = 1 << 20
+    max_positions: int = 0             # 0: config.json gives none; the position table's rows are what the file has
     learned_positions: bool = True
     torch_dtype: str = "bfloat16"
     extra: dict = field(default_factory=dict)
@@ -82,7 +82,7 @@ class VoseraxConfig:
                   eps=float(_need(norm, "eps", "norm")), layers=copy.deepcopy(_need(d, "layers", "the top level")),
                   residual_mult=1.0 if d.get("residual_mult") is None else d["residual_mult"],
                   streams=d.get("streams") or 0,
-                  max_positions=int(d.get("max_positions") or (1 << 20)),
+                  max_positions=int(d.get("max_positions") or 0),
                   learned_positions=bool(d.get("learned_positions", True)),
                   torch_dtype=d.get("torch_dtype") or "bfloat16",
                   extra={k: v for k, v in d.items() if k not in known})
@@ -92,8 +92,9 @@ class VoseraxConfig:
     def to_dict(self) -> dict:
         d = dict(self.extra)
         d.update(architecture="Voserax", vocab=self.vocab, width=self.width, norm={"eps": self.eps},
-                 residual_mult=self.residual_mult, layers=copy.deepcopy(self.layers), torch_dtype=self.torch_dtype,
-                 max_positions=self.max_positions)
+                 residual_mult=self.residual_mult, layers=copy.deepcopy(self.layers), torch_dtype=self.torch_dtype)
+        if self.max_positions:
+            d["max_positions"] = self.max_positions
         if self.streams:
             d["streams"] = self.streams
         if not self.learned_positions:
@@ -105,7 +106,8 @@ class VoseraxConfig:
     def validate(self) -> None:
         _positive_int(self.vocab, "vocab")
         _positive_int(self.width, "width")
-        _positive_int(self.max_positions, "max_positions")
+        if self.max_positions:
+            _positive_int(self.max_positions, "max_positions")
         if not (self.eps > 0 and math.isfinite(self.eps)):
             raise ConfigError(f"norm.eps must be positive, got {self.eps!r}")
         self.residual_mult = _number(self.residual_mult, "residual_mult")
@@ -187,7 +189,7 @@ class VoseraxConfig:
     # ---- derived ----------------------------------------------------------------
 
     def n_params(self) -> int:
-        return sum(math.prod(t.shape) for t in self.to_spec().tensors())
+        return sum(math.prod(t.shape) for t in self.to_spec().tensors() if -1 not in t.shape)   # (a table of unknown length is left out)
 
     def summary(self) -> str:
         kinds = "".join("-" if not l.get("mlp") else l["mlp"].get("kind", "dense")[0] for l in self.layers)
@@ -285,13 +287,13 @@ class VoseraxConfig:
                                     dict(streams=max(1, S), residual_mult=self.residual_mult)))
         emb_tensors = dict(table=TensorSpec("embed", (self.vocab, d)))
         if self.learned_positions:
-            emb_tensors["positions"] = TensorSpec("pos", (self.max_positions, d))
+            emb_tensors["positions"] = TensorSpec("pos", (self.max_positions or -1, d))
         return ModelSpec(
             architecture="Voserax", hidden_size=d, vocab_size=self.vocab,
             embedding=PartSpec("gather", dict(scale=None), emb_tensors),
             blocks=tuple(blocks), schedule=tuple(LayerCall(layer=i, cache=i) for i in range(len(blocks))),
             final_norm=PartSpec("rms_norm", dict(size=d, eps=eps), dict(gain=TensorSpec("final.norm", (d,), "vector"))),
             head=PartSpec("linear", dict(tied=True, softcap=None), {}),
-            max_positions=self.max_positions, stop_ids=(), storage_dtype=self.torch_dtype,
+            max_positions=self.max_positions or (1 << 20), stop_ids=(), storage_dtype=self.torch_dtype,
             default_sampling={}, residual_streams=max(1, S),
         )

@@ -98,6 +98,17 @@ __device__ __forceinline__ void moe_route_token(const float* z, float* s, float*
     for (int e = lane; e < E; e += 32)
       if (c[e] > best) best = c[e], bi = e;
     warp_argmax(best, bi);
+    if (bi >= E) {
+      // No score compares greater than -inf: the token's row holds a NaN (or every score is -inf).  That is
+      // reported (code 1); the lowest expert not chosen yet stands in, so that no index leaves its array.
+      bi = 0x7fffffff;
+      for (int e = lane; e < E; e += 32)
+        if (!(c[e] == -INFINITY) && e < bi) bi = e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) bi = min(bi, __shfl_xor_sync(0xffffffffu, bi, o));
+      if (bi >= E) bi = k % E;
+      if (lane == 0) llmx_report(1);
+    }
     if (lane == 0) c[bi] = -INFINITY;               // chosen: out of the running
     __syncwarp();
     const float sb = s[bi];
@@ -265,7 +276,16 @@ moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ pair_weig
   const int tid = threadIdx.x;
   for (int e = tid; e < E; e += blockDim.x) count[e] = 0;
   __syncthreads();
-  for (int r = tid; r < P; r += blockDim.x) atomicAdd(&count[ids[r]], 1);
+  // (an expert id outside 0..E-1 cannot come from this library's routing; it is reported, code 2, and counted as the
+  // last expert, so that no index leaves its array)
+  for (int r = tid; r < P; r += blockDim.x) {
+    int e = ids[r];
+    if ((unsigned)e >= (unsigned)E) {
+      llmx_report(2);
+      e = E - 1;
+    }
+    atomicAdd(&count[e], 1);
+  }
   __syncthreads();
   if (tid == 0) {
     int at = 0, tl = 0;
@@ -291,7 +311,8 @@ moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ pair_weig
   for (int tl = tile0[E] + tid; tl < max_tiles; tl += blockDim.x) tiles[3 * tl] = -1;
   __syncthreads();
   for (int r = tid; r < P; r += blockDim.x) {
-    const int e = ids[r];
+    int e = ids[r];
+    if ((unsigned)e >= (unsigned)E) e = E - 1;
     const int place = start[e] + atomicAdd(&count[e], 1);
     perm[place] = r;
     if (dest) {             // where the pair's result goes in [top, n_tokens, ...], and its weight, in sorted order

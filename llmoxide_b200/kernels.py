@@ -122,7 +122,7 @@ def _library(lib_name: str):
 # waited for a step anyway (no copy, no extra synchronisation).
 
 _STATUS_SLOTS = {"gemm_tc": 0, "attention_prefill_tc": 1, "attention_decode": 2, "sampling": 3, "moe_tc": 4,
-                 "short_conv": 5, "stream_mix": 6}
+                 "short_conv": 5, "stream_mix": 6, "moe": 7}
 _STATUS_MEANING = {
     "gemm_tc": {1: "the producer's wait for a free stage ran out", 2: "the MMA issuer's wait for a stage's data ran out",
                 3: "the epilogue's wait for an accumulator ran out", 4: "the MMA issuer's wait for a drained accumulator ran out",
@@ -137,6 +137,8 @@ _STATUS_MEANING = {
     "short_conv": {1: "a token's sequence, position, slot or page lies outside the launch's arrays",
                    2: "a sequence's rows or slot lie outside the launch's arrays (state update)"},
     "stream_mix": {1: "a wanted row lies outside the stream"},
+    "moe": {1: "a token's router scores hold a NaN (no expert compares greater than none)",
+            2: "an expert id outside the router's experts reached the sort"},
 }
 _status_host = None
 

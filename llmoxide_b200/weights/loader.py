@@ -47,7 +47,8 @@ def check_checkpoint(spec: ModelSpec, entries: dict, where="") -> list:
         e = entries.get(n)
         if e is None:
             continue
-        if tuple(e.shape) != tuple(t.shape):
+        if len(e.shape) != len(t.shape) or any(want not in (-1, got) for want, got in zip(t.shape, e.shape)):
+            # (-1 in the description: that extent is whatever the file has, e.g. a position table's rows)
             wrong.append((n, f"shape {list(e.shape)} != expected {list(t.shape)}"))
         elif t.role == "table" and e.dtype not in _INTS:
             wrong.append((n, f"dtype {e.dtype}, expected an integer table"))

@@ -159,3 +159,25 @@ def test_plain_routing_and_experts_against_closed_forms():
     W["m.correction"] = torch.tensor([-1.0, 0.0, 1.0], dtype=plain.F)
     out = plain.mixture(h, W, "m.", dict(router=dict(experts=1, top=2, identity=2), expert=dict(ff=d, limit=2.0)))
     assert torch.allclose(out, 2 * h / 3)       # the two identity experts, each with weight 1/3
+
+
+def test_without_max_positions_the_position_table_has_the_rows_the_file_has():
+    from llmoxide_b200.weights.loader import check_checkpoint
+
+    raw = copy.deepcopy(VX_D)
+    raw.pop("max_positions")
+    cfg = read_config(raw)
+    spec = cfg.to_spec()
+    assert [t.shape for t in spec.tensors() if t.name == "pos"] == [(-1, 64)] and "max_positions" not in cfg.to_dict()
+    assert "voserax" in cfg.summary()
+
+    class Entry:
+        def __init__(self, shape):
+            self.shape, self.dtype = shape, "BF16"
+
+    entries = {t.name: Entry(tuple(300 if n == -1 else n for n in t.shape)) for t in spec.tensors()}
+    assert check_checkpoint(spec, entries) == []
+    entries["pos"] = Entry((300, 65))
+    from llmoxide_b200.errors import WeightsError
+    with pytest.raises(WeightsError):
+        check_checkpoint(spec, entries)

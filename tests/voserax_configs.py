@@ -63,13 +63,16 @@ VX_C = dict(
         _attention(4, 1, 128, 128, 0.09, window=300, conv=2, rot=(128, 1000000.0), v_mix=True,
                    mlp=_moe(8, 2, 128, 1.0, identity=2, shared=(128, 1.0))),
     ])
-# No hyper-connections at all (plain residual sums times the factor), no learned ... everything optional left out.
+# No hyper-connections at all (plain residual sums times the factor); a layer without convolution, rotation or
+# window, and one whose window is a single token and whose router takes every expert.
 VX_D = dict(
     architecture="Voserax", vocab=130, width=64, norm=dict(eps=1e-5), residual_mult=0.9, max_positions=300,
     layers=[
         _attention(2, 2, 32, 32, 0.2, mlp=_dense(48)),
         _attention(2, 1, 32, 8, 0.2, window=1, conv=2, mlp=_moe(3, 3, 16, 1.0)),
     ])
+# Five streams, one key/value head, values wider than keys, top 4 of 9 + 4 identity experts, a layer without a
+# feed-forward in the middle, a window of five tokens.
 VX_E = dict(
     architecture="Voserax", vocab=160, width=72, norm=dict(eps=1e-5), residual_mult=0.7, streams=5, max_positions=300,
     layers=[
