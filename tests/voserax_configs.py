@@ -55,13 +55,13 @@ VX_B = dict(
     ])
 # The sizes the tiled kernels like (64 and 128, keys and values alike), one key/value head, two and five streams.
 VX_C = dict(
-    architecture="Voserax", vocab=512, width=256, norm=dict(eps=1e-6), residual_mult=0.8, streams=2, max_positions=1024,
+    architecture="Voserax", vocab=500, width=256, norm=dict(eps=1e-6), residual_mult=0.8, streams=2, max_positions=1024,
     layers=[
         _attention(4, 1, 128, 128, 0.09, window=100, conv=4, rot=(64, 10000.0), scaling=(2.0, 256, 32.0, 1.0), v_mix=True,
-                   mlp=_moe(8, 2, 128, 1.0, identity=2, shared=(128, 1.0))),
+                   mlp=_moe(12, 2, 128, 1.25, identity=1, shared=(128, 1.25))),
         _attention(4, 2, 64, 64, 0.12, window=70, conv=4, rot=(64, 10000.0), mlp=_dense(256)),
         _attention(4, 1, 128, 128, 0.09, window=300, conv=2, rot=(128, 1000000.0), v_mix=True,
-                   mlp=_moe(8, 2, 128, 1.0, identity=2, shared=(128, 1.0))),
+                   mlp=_moe(12, 2, 128, 1.25, identity=1, shared=(128, 1.25))),
     ])
 # No hyper-connections at all (plain residual sums times the factor); a layer without convolution, rotation or
 # window, and one whose window is a single token and whose router takes every expert.
@@ -76,9 +76,9 @@ VX_D = dict(
 VX_E = dict(
     architecture="Voserax", vocab=160, width=72, norm=dict(eps=1e-5), residual_mult=0.7, streams=5, max_positions=300,
     layers=[
-        _attention(3, 1, 24, 40, 0.3, window=40, conv=4, rot=(12, 10000.0), scaling=(8.0, 32, 4.0, 1.0), v_mix=True,
+        _attention(3, 1, 24, 40, 0.3, window=41, conv=4, rot=(12, 10000.0), scaling=(8.0, 32, 4.0, 1.0), v_mix=True,
                    mlp=_moe(9, 4, 24, 1.0, identity=4, shared=(16, 1.0))),
-        _attention(3, 1, 24, 40, 0.3, window=40, conv=4, rot=(12, 10000.0), scaling=(8.0, 32, 4.0, 1.0), v_mix=True,
+        _attention(3, 1, 24, 40, 0.3, window=41, conv=4, rot=(12, 10000.0), scaling=(8.0, 32, 4.0, 1.0), v_mix=True,
                    mlp=None),
         _attention(3, 1, 24, 40, 0.3, window=5, conv=4, rot=(12, 10000.0), v_mix=True, mlp=_dense(30)),
     ])
