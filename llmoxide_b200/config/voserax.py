@@ -212,9 +212,11 @@ class VoseraxConfig:
                            v_conv=TensorSpec(p + "v.conv", (G * Dv, taps), "vector", (0.0, 0.5)))
         v_mix = None
         if m.get("v_mix"):
-            # the first layer that mixes gives its values to the later ones; its own weight is stored but unused
+            # the first layer that mixes gives its values to the later ones; its own weight, if a file stores one, is
+            # unused (and ignored)
             v_mix = "source" if first_mixing is None else "mix"
-            tensors["v_mix"] = TensorSpec(p + "vmix", (), "vector", (0.5, 0.1))
+            if v_mix == "mix":
+                tensors["v_mix"] = TensorSpec(p + "vmix", (), "vector", (0.5, 0.1))
         mixer = PartSpec("gqa_attention", dict(
             hidden_size=d, n_heads=H, n_kv_heads=G, head_dim=D, v_head_dim=Dv, scale=float(m["scale"]),
             window=mask["size"] if mask else None, keep_first=0, qk_norm_eps=None, own_kv=True,
@@ -285,6 +287,15 @@ class VoseraxConfig:
                             hc_mix=TensorSpec(f"{p}{q}.mix", (S, S), "vector", (1.0 / S, 0.1 / S))))
             blocks.append(BlockSpec("hyper_connections", mixer, ffn, norms, position,
                                     dict(streams=max(1, S), residual_mult=self.residual_mult)))
+        # What a file may carry although this configuration does not use it (a weight of a switched-off option):
+        # left alone, not an error.
+        used = {t.name for b in blocks for part in (b.mixer, b.feed_forward, *b.norms.values()) for t in part.tensors.values()}
+        optional = []
+        for i in range(len(blocks)):
+            p = f"l{i}."
+            optional += [p + "mix.vmix", p + "mix.q.conv", p + "mix.k.conv", p + "mix.v.conv", p + "norm2", p + "mlp.correction"]
+            optional += [f"{p}{q}.{w}" for q in ("hc1", "hc2") for w in ("in", "out", "mix")]
+        ignored = tuple(n for n in optional if n not in used) + (() if self.learned_positions else ("pos",))
         emb_tensors = dict(table=TensorSpec("embed", (self.vocab, d)))
         if self.learned_positions:
             emb_tensors["positions"] = TensorSpec("pos", (self.max_positions or -1, d))
@@ -295,5 +306,5 @@ class VoseraxConfig:
             final_norm=PartSpec("rms_norm", dict(size=d, eps=eps), dict(gain=TensorSpec("final.norm", (d,), "vector"))),
             head=PartSpec("linear", dict(tied=True, softcap=None), {}),
             max_positions=self.max_positions or (1 << 20), stop_ids=(), storage_dtype=self.torch_dtype,
-            default_sampling={}, residual_streams=max(1, S),
+            default_sampling={}, residual_streams=max(1, S), ignored_tensors=ignored,
         )

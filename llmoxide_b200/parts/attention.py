@@ -91,9 +91,8 @@ class GQAttention:
             # [channels of q | k | v, taps] -> tap-major [taps, channels]: a warp reads neighbouring channels of a tap
             self.conv_w = torch.cat([weights.pop(t[r].name).to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")],
                                     dim=0).t().contiguous()
-        if self.v_mix:
-            lam = weights.pop(t["v_mix"].name).to(torch.float32).reshape(1).contiguous()
-            self.v_lambda = lam if self.v_mix == "mix" else None      # the source's own weight is unused
+        if self.v_mix == "mix":
+            self.v_lambda = weights.pop(t["v_mix"].name).to(torch.float32).reshape(1).contiguous()
         # the projection's rows go through the convolution kernel (which also rotates, mixes and writes the cache)
         self.staged = bool(self.taps or self.v_mix)
         self.channels = (self.H + self.G) * self.D + self.G * self.Dv

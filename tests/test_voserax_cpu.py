@@ -31,7 +31,8 @@ def test_description_names_every_tensor_once_with_the_shapes_of_the_configuratio
     assert shapes["embed"] == (211, 96) and shapes["pos"] == (512, 96) and "head" not in shapes
     assert shapes["l0.mix.q"] == (4 * 32, 96) and shapes["l0.mix.v"] == (2 * 16, 96) and shapes["l0.mix.o"] == (96, 4 * 16)
     assert shapes["l0.mix.q.conv"] == (128, 3) and shapes["l2.mix.k.conv"] == (48, 2) and shapes["l2.mix.v.conv"] == (32, 2)
-    assert shapes["l1.mix.vmix"] == () and "l0.mix.vmix" not in shapes and "l2.mix.vmix" not in shapes
+    assert shapes["l3.mix.vmix"] == () and not any(f"l{i}.mix.vmix" in shapes for i in (0, 1, 2))   # 1 is the source
+    assert spec.is_ignored("l1.mix.vmix") and spec.is_ignored("l2.norm2") and not spec.is_ignored("l3.mix.vmix")
     assert shapes["l0.mlp.gate"] == (72, 96) and shapes["l1.mlp.router"] == (8, 96) and shapes["l1.mlp.correction"] == (8,)
     assert shapes["l1.mlp.e5.down"] == (96, 40) and "l1.mlp.e6.gate" not in shapes          # 6 experts + 2 identity
     assert shapes["l1.mlp.shared.sg"] == (1, 96) and shapes["l1.mlp.shared.up"] == (24, 96)
