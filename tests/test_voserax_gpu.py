@@ -37,7 +37,7 @@ def _i32(x):
 # copies of the residual stream
 # ---------------------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("S, d, n_split", [(1, 40, 1), (2, 96, 3), (4, 192, 1), (5, 1000, 2), (8, 64, 1)])
+@pytest.mark.parametrize("S, d, n_split", [(1, 40, 1), (2, 96, 3), (4, 200, 5), (5, 1000, 2), (8, 64, 1), (3, 50, 6), (2, 2050, 1), (4, 2048, 3)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_stream_update_and_norm_against_the_plain_sublayer(S, d, n_split, out_dtype):
     from llmoxide_b200 import kernels
