@@ -8,7 +8,8 @@
 // u of the positions before the step's first token comes from the sequence's state: the last taps-1 projected
 // rows, float32 [slot][taps-1][C], oldest first (zero-filled when the slot gets its owner, which is also what
 // positions before the start must read).  conv_state_update moves the state on by the step's tokens; it is a
-// second kernel because the first one's CTAs still read the old state.
+// second kernel because the first one's CTAs still read the old state.  In a step in which every sequence brings
+// one token (`inline_state`) the first kernel moves the state on itself.
 //
 // Row layout of the projection: q heads (H of D), k heads (G of D), v heads (G of Dv); C = (H+G) D + G Dv.
 // One warp per (token, head).  The convolved head is staged in shared memory so that a dim can read its
@@ -65,7 +66,7 @@ __device__ __forceinline__ void sc_value4(const TIN* p, int n_split, size_t spli
 // fetched once for all of them; a step of few tokens gives every head a warp of its own.
 template <typename TIN, typename TA, typename TC, bool VEC, int SPW>
 __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split, size_t split_stride,
-                                       const float* __restrict__ state, const float* __restrict__ conv_w, int taps,
+                                       float* state, int inline_state, const float* __restrict__ conv_w, int taps,
                                        TA* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                                        const int* __restrict__ block_table, int table_width,
                                        const int* __restrict__ token_seq, const int* __restrict__ token_pos,
@@ -95,7 +96,12 @@ __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split
     if (lane == 0) llmx_report(1);
     return;
   }
-  const float* st = taps > 1 ? state + (size_t)slot * (taps - 1) * C : nullptr;
+  float* st = taps > 1 ? state + (size_t)slot * (taps - 1) * C : nullptr;
+  // A step in which this sequence brings one token: the warp that convolves a head is the only reader of that
+  // head's channels of the state, so it moves them on itself (row j of the old state becomes row j - 1, the token's
+  // own projected row the last) and the second kernel is not launched.  A thread writes a row only after it has
+  // read it and the one behind it.
+  float* st_new = (inline_state && st && pos == p0 && seq_start[b + 1] - row0 == 1) ? st : nullptr;
   const float lam = v_mix_mode == 2 ? v_lambda[0] : 0.f;
   float* buf = head_buf + warp * max(D, Dv);
   pdl_wait();
@@ -128,6 +134,7 @@ __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
             if (j0 + jj < taps) {
+              if (st_new && j0 + jj >= 1) sc_store4(st_new + (size_t)(j0 + jj - 1) * C + c, u[jj]);
               float w[4];
               sc_load4(wp + (size_t)(j0 + jj) * C, w);
 #pragma unroll
@@ -191,6 +198,7 @@ __global__ void conv_rope_cache_kernel(const TIN* __restrict__ proj, int n_split
         float u = 0.f;
         if (pp >= p0) u = sc_value(proj + (size_t)(row0 + pp - p0) * C + c, n_split, split_stride);
         else if (pp >= 0) u = st[(size_t)(pp - (p0 - (taps - 1))) * C + c];
+        if (st_new && j >= 1) st_new[(size_t)(j - 1) * C + c] = u;
         y = fmaf(conv_w[(size_t)j * C + c], u, y);
       }
     } else {
@@ -262,9 +270,10 @@ __global__ void conv_state_update_kernel(const TIN* __restrict__ proj, int n_spl
 
 // proj [T, C] or n_split float32 partials; conv_w float32 [taps, C] (taps 0: no convolution); state float32
 // [slots, taps-1, C]; q_out [T, H*D]; cos/sin float32 [positions, n_rot/2]; v_first float32 [T, G*Dv] (v_mix_mode
-// 1: written, 2: read with the weight *v_lambda).
-LLMX_API int llmx_conv_rope_cache(const void* proj, int in_dtype, int n_split, long long split_stride, const float* state,
-                                  const float* conv_w, int taps, void* q_out, int act_dtype, void* k_cache, void* v_cache,
+// 1: written, 2: read with the weight *v_lambda).  inline_state: sequences that bring exactly one token have their
+// state moved on by this kernel (the caller then leaves llmx_conv_state_update out; every sequence must bring one).
+LLMX_API int llmx_conv_rope_cache(const void* proj, int in_dtype, int n_split, long long split_stride, float* state,
+                                  int inline_state, const float* conv_w, int taps, void* q_out, int act_dtype, void* k_cache, void* v_cache,
                                   int cache_dtype, const int* block_table, int table_width, const int* token_seq,
                                   const int* token_pos, const int* seq_start, const int* seq_past, const int* seq_slot,
                                   const float* cos_t, const float* sin_t, int n_rot, float* v_first, const float* v_lambda,
@@ -292,7 +301,7 @@ LLMX_API int llmx_conv_rope_cache(const void* proj, int in_dtype, int n_split, l
   } while (0)
 #define GO2(TIN, TA, TC, VEC, SPW)                                                                                      \
   launch_pdl(conv_rope_cache_kernel<TIN, TA, TC, VEC, SPW>, grid, dim3(SC_WARPS * 32), smem, stream, (const TIN*)proj, n_split, \
-             (size_t)split_stride, state, conv_w, taps, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,           \
+             (size_t)split_stride, state, inline_state, conv_w, taps, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,           \
              table_width, token_seq, token_pos, seq_start, seq_past, seq_slot, cos_t, sin_t, n_rot, v_first, v_lambda, \
              v_mix_mode, H, G, D, Dv, n_tokens, n_seqs, n_slots, (int)n_pages)
 #define CASE(TIN, TA, TC)              \

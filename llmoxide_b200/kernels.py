@@ -280,12 +280,13 @@ def stream_mix_norm(h, delta, mix, write, read, gain, eps: float, out, rows=None
 
 def conv_rope_cache(proj, state, conv_w, taps: int, q_out, k_cache, v_cache, block_table, ctx, cos, sin, n_rot: int,
                     v_first, v_lambda, v_mix_mode: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                    v_head_dim: int) -> None:
+                    v_head_dim: int, inline_state: bool = False) -> None:
     """A short causal convolution (``conv_w`` float32 [taps, C], tap-major; taps 0: none) over the fused q|k|v projection
     ``proj`` ([T,C] or float32 partials [P,T,C]) with the sequences' earlier rows from ``state`` float32
     [slots, taps-1, C]; then q and k rotated (q to ``q_out`` [T,H*D], k to the cache) and v written to the cache:
     as it is (``v_mix_mode`` 0), also copied to ``v_first`` float32 [T,G*Dv] (1), or mixed with it as
-    (1 - l) v + l v_first, l = ``v_lambda[0]`` (2).  ``ctx``: the step's index arrays."""
+    (1 - l) v + l v_first, l = ``v_lambda[0]`` (2).  ``ctx``: the step's index arrays.  ``inline_state``: every
+    sequence brings exactly one token, and the kernel moves the state on itself (no ``conv_state_update`` then)."""
     _dev(proj, state, conv_w, q_out, k_cache, v_cache, block_table, cos, sin, v_first, v_lambda)
     _contig("proj", proj), _contig("q_out", q_out), _contig("block_table", block_table)
     n_split, stride = (proj.shape[0], proj.stride(0)) if proj.dim() == 3 else (1, 0)
@@ -300,10 +301,10 @@ def conv_rope_cache(proj, state, conv_w, taps: int, q_out, k_cache, v_cache, blo
     if v_mix_mode:
         assert v_first.dtype == torch.float32 and v_first.shape == (T, n_kv_heads * v_head_dim) and v_first.is_contiguous()
     f = _fn("short_conv", "llmx_conv_rope_cache",
-            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p])
-    _check(f(_ptr(proj), _tag(proj), n_split, stride, _ptr(state), _ptr(conv_w), taps, _ptr(q_out), _tag(q_out),
+    _check(f(_ptr(proj), _tag(proj), n_split, stride, _ptr(state), int(bool(inline_state) and taps > 1), _ptr(conv_w), taps, _ptr(q_out), _tag(q_out),
              _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table), block_table.shape[1], _ptr(ctx.token_seq),
              _ptr(ctx.token_pos), _ptr(ctx.seq_start), _ptr(ctx.seq_past), _ptr(ctx.seq_slot), _ptr(cos), _ptr(sin), n_rot,
              _ptr(v_first), _ptr(v_lambda), v_mix_mode, T, n_heads, n_kv_heads, head_dim, v_head_dim, ctx.n_seqs,

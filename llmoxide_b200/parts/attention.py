@@ -142,9 +142,12 @@ class GQAttention:
                 mode = 1
             elif self.v_mix == "mix":
                 v_first, mode = ctx.carry[self.v_mix_key], 2
+            # a step of single tokens moves the convolution's state on inside the same kernel
+            inline = bool(ctx.is_decode and self.taps > 1)
             kernels.conv_rope_cache(qkv, view.state, self.conv_w, self.taps, q, view.k, view.v, block_table, ctx, cos, sin,
-                                    n_rot, v_first, self.v_lambda, mode, H, G, D, Dv)
-            kernels.conv_state_update(qkv, view.state, self.taps, ctx)
+                                    n_rot, v_first, self.v_lambda, mode, H, G, D, Dv, inline_state=inline)
+            if not inline:
+                kernels.conv_state_update(qkv, view.state, self.taps, ctx)
         elif not writes_cache and self.q_gain is None and n_rot == 0:
             # A call that reads another call's cache entry makes only queries; nothing is done to them.
             q = self.q_only(x, out_dtype=self.rt.act_dtype)

@@ -141,10 +141,13 @@ def _conv_case(cuts, H, G, D, Dv, taps, n_rot, mode, dtype, n_split=1, seed=0):
             vf = torch.zeros((T, G * Dv), dtype=torch.float32, device=DEV)
         elif mode == 2:
             vf = torch.cat([first[b][past[b] : past[b] + c[b]] for b in live]).float().to(DEV).contiguous()
+        single = all(c[b] == 1 for b in live)       # a step of single tokens: the first kernel moves the state on itself
         kernels.conv_rope_cache(proj, state, w.float().t().contiguous().to(DEV) if taps else None, taps, q, kc, vc,
                                 table[live].to(DEV).contiguous(), ctx, cos, sin, n_rot, vf,
-                                torch.tensor([lam], dtype=torch.float32, device=DEV) if mode == 2 else None, mode, H, G, D, Dv)
-        kernels.conv_state_update(proj, state, taps, ctx)
+                                torch.tensor([lam], dtype=torch.float32, device=DEV) if mode == 2 else None, mode, H, G, D, Dv,
+                                inline_state=single)
+        if not single:
+            kernels.conv_state_update(proj, state, taps, ctx)
         at = 0
         for b in live:
             got_q[b][past[b] : past[b] + c[b]] = q[at : at + c[b]].float().cpu()
